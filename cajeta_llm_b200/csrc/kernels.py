@@ -171,7 +171,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
     ([G + 1] int32) ``w`` is [G, N, K], output row s belongs to the group whose range
     holds s, and ``a_row_index[s]`` names the row of ``a`` that feeds it.
     """
-    _need(a, "a"), _need(w, "w"), _need(out, "out")
+    _need(w, "w"), _need(out, "out")
+    if not a.is_cuda or a.dim() != 2 or a.stride(1) != 1:
+        raise KernelError("gemm: a must be a CUDA matrix whose rows are contiguous (a column slice of a wider one is fine)")
     grouped = group_offsets is not None
     N, K = w.shape[-2], w.shape[-1]
     M = rows if rows is not None else out.shape[0]
@@ -222,12 +224,13 @@ def head_prepare(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: tor
                  v_plane: Optional[torch.Tensor], positions: torch.Tensor, row_req: Optional[torch.Tensor],
                  table: Optional[torch.Tensor], page_tokens: int, n_heads: int, n_kv: int, head_dim: int, value_dim: int,
                  rotary_dim: int, inv_freq: Optional[torch.Tensor], magnitude: float, q_norm: Optional[torch.Tensor],
-                 k_norm: Optional[torch.Tensor], eps: float, write_kv: bool) -> None:
+                 k_norm: Optional[torch.Tensor], eps: float, write_kv: bool, norm_whole: bool = False) -> None:
     """Queries, keys and values of a step's rows (x float32 [T, ld], columns from q_off, k_off, v_off) made ready
     for attention: an RMS norm over each head of q and k (when ``q_norm`` / ``k_norm``, float32 [head_dim], are
     given), the rotation of their first ``rotary_dim`` entries (entry i with i + rotary_dim / 2; cos and sin times
     ``magnitude``), q to ``q_out``, k and v into the cache pages of the row's request.  ``v_off`` < 0: the
-    values are the keys as projected, before norm and rotation."""
+    values are the keys as projected, before norm and rotation.  ``norm_whole``: one statistic over all heads of q
+    (of k) at once, and weights of ``n_heads * head_dim`` (``n_kv * head_dim``) entries."""
     _need(x, "x", torch.float32), _need(q_out, "q_out"), _need(positions, "positions", torch.int32)
     cache_dtype = _code(q_out)
     if write_kv:
@@ -238,11 +241,13 @@ def head_prepare(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: tor
     for n, t in (("q_norm", q_norm), ("k_norm", k_norm), ("inv_freq", inv_freq)):
         if t is not None:
             _need(t, n, torch.float32)
+    if norm_whole and ((q_norm is not None and q_norm.numel() != n_heads * head_dim) or (k_norm is not None and k_norm.numel() != n_kv * head_dim)):
+        raise KernelError("head_prepare: a norm over the whole projection takes weights of heads * head_dim entries")
     st = library("attention_paged").cj_head_prepare(
         _ptr(x), _i(x.stride(0)), _i(q_off), _i(k_off), _i(v_off), _ptr(q_out), _i(_code(q_out)), _ptr(k_plane), _ptr(v_plane),
         _i(cache_dtype), _ptr(positions), _ptr(row_req), _ptr(table), _i(table.stride(0) if table is not None else 0),
         _i(page_tokens), _i(x.shape[0]), _i(n_heads), _i(n_kv), _i(head_dim), _i(value_dim), _i(rotary_dim), _ptr(inv_freq),
-        _f(magnitude), _ptr(q_norm), _ptr(k_norm), _f(eps), _i(1 if write_kv else 0), _stream())
+        _f(magnitude), _ptr(q_norm), _ptr(k_norm), _f(eps), _i(1 if write_kv else 0), _i(1 if norm_whole else 0), _stream())
     _check(st, "head_prepare")
 
 
@@ -272,6 +277,28 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v
         _ptr(row_req), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim),
         _i(value_dim or head_dim), _i(window), _f(scale), _f(softcap), gate_ptr, _i(gate_ld), _stream())
     _check(st, "paged_attention")
+
+
+def mixed_heads_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                          positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
+                          n_heads: int, n_kv: int, head_dim: int, value_dim: int, window: int, scale: float,
+                          temp: Optional[torch.Tensor] = None, talk: Optional[torch.Tensor] = None,
+                          sink: Optional[torch.Tensor] = None) -> None:
+    """Attention of every row over its request's cached keys [from, position] in which the heads' scores are mixed
+    before the softmax: raw_g = (q_g . k) scale temp[g]; s_h = sum_g talk[h, g] raw_g; the softmax's divisor also
+    holds exp(sink[h]).  ``temp`` [heads], ``talk`` [heads, heads], ``sink`` [heads]: float32, each optional."""
+    _need(q, "q"), _need(out, "out"), _need(k_plane, "k_plane"), _need(v_plane, "v_plane")
+    _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
+    for n, t, size in (("temp", temp, n_heads), ("talk", talk, n_heads * n_heads), ("sink", sink, n_heads)):
+        if t is not None:
+            _need(t, n, torch.float32)
+            if t.numel() != size:
+                raise KernelError(f"mixed_heads_attention: {n} must hold {size} entries, found {t.numel()}")
+    st = library("attention_paged").cj_mixed_heads_attention(
+        _ptr(q), _ptr(out), _i(_code(q)), _ptr(k_plane), _ptr(v_plane), _i(_code(k_plane)), _ptr(positions),
+        _ptr(row_req), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(q.shape[0]), _i(n_heads), _i(n_kv), _i(head_dim),
+        _i(value_dim or head_dim), _i(window), _f(scale), _ptr(temp), _ptr(talk), _ptr(sink), _stream())
+    _check(st, "mixed_heads_attention")
 
 
 def _route_mode(norm_topk: bool, sigmoid_scores: bool, groups) -> int:
@@ -499,44 +526,47 @@ def scale_rows_gather(x: torch.Tensor, slot_of_pick: torch.Tensor, weights: torc
 
 def short_conv(x: torch.Tensor, x_offset: int, channels: int, taps: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
                state: torch.Tensor, row_req: torch.Tensor, req_start: torch.Tensor, req_slot: torch.Tensor,
-               out: torch.Tensor, activate: bool = True) -> None:
+               out: torch.Tensor, activate: bool = True, state_offset: int = 0) -> None:
     """Causal convolution per channel over columns [x_offset, x_offset + channels) of x (float32 [T, ld]):
     out[r, c] = act(bias[c] + sum_j weight[c, taps-1-j] * x[r - j, c]), where rows before the
-    request's first row of this step come from ``state`` ([slots, n] float32, whose first
-    (taps-1) * channels entries per slot are the request's last inputs, oldest first)."""
+    request's first row of this step come from ``state`` ([slots, n] float32, whose
+    (taps-1) * channels entries per slot from ``state_offset`` on are the request's last inputs, oldest first)."""
     _need(x, "x", torch.float32), _need(weight, "weight", torch.float32), _need(state, "state", torch.float32), _need(out, "out")
     for n, t in (("row_req", row_req), ("req_start", req_start), ("req_slot", req_slot)):
         _need(t, n, torch.int32)
     if bias is not None:
         _need(bias, "bias", torch.float32)
-    if weight.shape != (channels, taps) or x.shape[1] < x_offset + channels or out.shape[1] < channels or state[0].numel() < (taps - 1) * channels:
+    if weight.shape != (channels, taps) or x.shape[1] < x_offset + channels or out.shape[1] < channels or state[0].numel() < state_offset + (taps - 1) * channels:
         raise KernelError("short_conv: sizes do not agree")
-    st = library("recurrent").cj_short_conv(ctypes.c_void_p(x.data_ptr() + 4 * x_offset), _i(x.stride(0)), _i(channels), _i(taps), _ptr(weight), _ptr(bias), _ptr(state),
+    st = library("recurrent").cj_short_conv(ctypes.c_void_p(x.data_ptr() + 4 * x_offset), _i(x.stride(0)), _i(channels), _i(taps), _ptr(weight), _ptr(bias),
+                                            ctypes.c_void_p(state.data_ptr() + 4 * state_offset),
                                             _ll(state.stride(0)), _ptr(row_req), _ptr(req_start), _ptr(req_slot), _ptr(out),
                                             _i(out.stride(0)), _i(_code(out)), _i(1 if activate else 0), _i(x.shape[0]), _stream())
     _check(st, "short_conv")
 
 
 def short_conv_commit(x: torch.Tensor, x_offset: int, channels: int, taps: int, state: torch.Tensor, req_start: torch.Tensor,
-                      req_slot: torch.Tensor, requests: int) -> None:
+                      req_slot: torch.Tensor, requests: int, state_offset: int = 0) -> None:
     """After ``short_conv``: every request's last taps-1 inputs (of this step, and of the state
     where the step brought fewer) become its state."""
     _need(x, "x", torch.float32), _need(state, "state", torch.float32)
     _need(req_start, "req_start", torch.int32), _need(req_slot, "req_slot", torch.int32)
     if taps <= 1:
         return
-    st = library("recurrent").cj_short_conv_commit(ctypes.c_void_p(x.data_ptr() + 4 * x_offset), _i(x.stride(0)), _i(channels), _i(taps), _ptr(state),
+    st = library("recurrent").cj_short_conv_commit(ctypes.c_void_p(x.data_ptr() + 4 * x_offset), _i(x.stride(0)), _i(channels), _i(taps),
+                                                   ctypes.c_void_p(state.data_ptr() + 4 * state_offset),
                                                    _ll(state.stride(0)), _ptr(req_start), _ptr(req_slot), _i(requests), _stream())
     _check(st, "short_conv_commit")
 
 
-SCAN_SSD, SCAN_DELTA = 0, 1
+SCAN_SSD, SCAN_DELTA, SCAN_GLA, SCAN_MLSTM = 0, 1, 2, 3
 
 
-def state_scan_floats(heads: int, rows: int, cols: int) -> int:
+def state_scan_floats(heads: int, rows: int, cols: int, mode: int = SCAN_SSD) -> int:
     """float32 entries of per-request state that ``state_scan`` needs for ``heads`` matrices of
-    rows x cols: the scan keeps them in the order its threads hold them (padded to whole tiles).
-    The same arithmetic as the kernel library's ``cj_state_scan_floats`` (tested equal)."""
+    rows x cols: the scan keeps them in the order its threads hold them (padded to whole tiles;
+    ``SCAN_MLSTM`` keeps a vector over the rows and a scalar beside every tile).
+    The same arithmetic as the kernel library's ``cj_state_scan_floats_mode`` (tested equal)."""
     dp = 4
     while dp < 32 and dp < rows and (dp < 8 or heads * cols * dp // 32 < 592):
         dp <<= 1
@@ -547,13 +577,14 @@ def state_scan_floats(heads: int, rows: int, cols: int) -> int:
     while nper < per:
         nper <<= 1
     cols_per_block = 4 * (32 // dp)
-    return heads * -(-cols // cols_per_block) * nper * 128
+    tile = (2 * nper + 1) * 128 if mode == SCAN_MLSTM else nper * 128
+    return heads * -(-cols // cols_per_block) * tile
 
 
 def state_scan(mode: int, x: torch.Tensor, off_a: int, off_b: int, off_v: int, raw: torch.Tensor, off_dt: int, off_beta: int,
-               A_log: torch.Tensor, dt_bias: torch.Tensor, skip: Optional[torch.Tensor], state: torch.Tensor, state_offset: int,
-               req_start: torch.Tensor, req_slot: torch.Tensor, out: torch.Tensor, requests: int, heads: int, groups: int,
-               rows: int, cols: int, q_scale: float = 1.0) -> None:
+               A_log: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor], skip: Optional[torch.Tensor], state: torch.Tensor,
+               state_offset: int, req_start: torch.Tensor, req_slot: torch.Tensor, out: torch.Tensor, requests: int, heads: int,
+               groups: int, rows: int, cols: int, q_scale: float = 1.0, c0: float = 0.0, c1: float = 0.0) -> None:
     """Walks every request's rows of the step in order through its recurrent state
     (``state[slot, state_offset:]``, ``state_scan_floats(heads, rows, cols)`` float32 entries in the
     scan's own layout; zero = the empty state) and writes a row's
@@ -563,34 +594,69 @@ def state_scan(mode: int, x: torch.Tensor, off_a: int, off_b: int, off_v: int, r
     off_dt + h = the step size before softplus.  S = exp(-exp(A_log) dt) S + dt B x^T; y = S^T C + skip x.
     ``SCAN_DELTA``: off_a = q [groups, rows], off_b = k, off_v = v; raw columns off_dt + h (decay input)
     and off_beta + h.  q and k become unit vectors (q times ``q_scale``); S = g S; u = beta (v - S^T k);
-    S += k u^T; o = S^T q."""
+    S += k u^T; o = S^T q.
+    ``SCAN_GLA``: off_a = q [heads, rows] (times ``q_scale``), off_b = k, off_v = v; raw columns off_dt + h * rows + d = z,
+    the decays' inputs; alpha = sigmoid(z)^c0 (c0 = 1 / tau); S = diag(alpha) S + k v^T; o = S^T q.
+    ``SCAN_MLSTM``: off_a = q (times ``q_scale``), off_b = k, off_v = v; raw columns off_dt + h and off_beta + h = the
+    input and forget gates before their bias (``dt_bias`` = the input gate's, ``A_log`` = the forget gate's);
+    i = c0 tanh((. + b) / c0), f = log sigmoid(c0 tanh((. + b) / c0)); m_t = max(f + m, i), m_0 = 0;
+    S = e^(f + m - m_t) S + e^(i - m_t) k v^T, n likewise with k alone; o = S^T q / (max(|n . q|, e^(-m_t)) + c1)."""
     _need(x, "x", torch.float32), _need(raw, "raw", torch.float32), _need(state, "state", torch.float32), _need(out, "out", torch.float32)
-    _need(A_log, "A_log", torch.float32), _need(dt_bias, "dt_bias", torch.float32)
+    if mode != SCAN_GLA:
+        _need(A_log, "A_log", torch.float32), _need(dt_bias, "dt_bias", torch.float32)
     _need(req_start, "req_start", torch.int32), _need(req_slot, "req_slot", torch.int32)
     if skip is not None:
         _need(skip, "skip", torch.float32)
-    if state[0].numel() < state_offset + state_scan_floats(heads, rows, cols) or out.shape[1] != heads * cols:
+    if state[0].numel() < state_offset + state_scan_floats(heads, rows, cols, mode) or out.shape[1] != heads * cols:
         raise KernelError("state_scan: state or out too small")
     st = library("recurrent").cj_state_scan(
         _i(mode), _ptr(x), _i(x.stride(0)), _i(off_a), _i(off_b), _i(off_v), _ptr(raw), _i(raw.stride(0)), _i(off_dt), _i(off_beta),
         _ptr(A_log), _ptr(dt_bias), _ptr(skip), ctypes.c_void_p(state.data_ptr() + 4 * state_offset), _ll(state.stride(0)),
-        _ll(state[0].numel() - state_offset), _ptr(req_start), _ptr(req_slot), _ptr(out), _i(requests), _i(heads), _i(groups), _i(rows), _i(cols), _f(q_scale), _stream())
+        _ll(state[0].numel() - state_offset), _ptr(req_start), _ptr(req_slot), _ptr(out), _i(requests), _i(heads), _i(groups), _i(rows), _i(cols), _f(q_scale), _f(c0), _f(c1), _stream())
     _check(st, "state_scan")
 
 
 def gated_group_norm(y: torch.Tensor, part_len: int, z: torch.Tensor, z_offset: int, weight: torch.Tensor, eps: float,
-                     gate_first: bool, out: torch.Tensor) -> None:
+                     gate_first: bool, out: torch.Tensor, sigmoid_gate: bool = False) -> None:
     """Rows of y (float32 [T, n]) in parts of ``part_len``: RMS norm of each part times weight
     (indexed by column modulo its length) and times silu(z[:, z_offset + column]); the gate is
-    applied before the norm's statistics when ``gate_first``, after the norm otherwise."""
+    applied before the norm's statistics when ``gate_first``, after the norm otherwise.  ``sigmoid_gate``: the
+    gate is sigmoid(z) instead of silu(z)."""
     _need(y, "y", torch.float32), _need(z, "z", torch.float32), _need(weight, "weight", torch.float32), _need(out, "out")
     T, n = y.shape
     if out.shape != y.shape or z.shape[1] < z_offset + n:
         raise KernelError("gated_group_norm: sizes do not agree")
     st = library("recurrent").cj_gated_group_norm(_ptr(y), _i(n), _i(part_len), ctypes.c_void_p(z.data_ptr() + 4 * z_offset),
                                                   _i(z.stride(0)), _ptr(weight), _i(weight.numel()), _f(eps),
-                                                  _i(1 if gate_first else 0), _ptr(out), _i(_code(out)), _i(T), _stream())
+                                                  _i((1 if gate_first else 0) | (2 if sigmoid_gate else 0)), _ptr(out), _i(_code(out)), _i(T), _stream())
     _check(st, "gated_group_norm")
+
+
+def rmsnorm_mix2(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, eps: float, coef: float, out: torch.Tensor,
+                 accumulate: bool = False) -> None:
+    """out (+)= coef (a / rms(a) * wa + b / rms(b) * wb), row by row; everything float32."""
+    for n, t in (("a", a), ("wa", wa), ("b", b), ("wb", wb), ("out", out)):
+        _need(t, n, torch.float32)
+    rows, H = a.shape
+    if b.shape != a.shape or out.shape != a.shape or wa.numel() != H or wb.numel() != H:
+        raise KernelError("rmsnorm_mix2: shapes do not agree")
+    st = library("recurrent").cj_rmsnorm_mix2(_ptr(a), _ptr(wa), _ptr(b), _ptr(wb), _f(eps), _f(coef), _i(1 if accumulate else 0),
+                                              _ptr(out), _i(rows), _i(H), _stream())
+    _check(st, "rmsnorm_mix2")
+
+
+def relu2_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(x, 0)^2 in out's dtype; x float32."""
+    _need(x, "x", torch.float32), _need(out, "out")
+    if out.numel() != x.numel():
+        raise KernelError("relu2_rows: sizes differ")
+    _check(library("recurrent").cj_relu2_rows(_ptr(x), _ptr(out), _i(_code(out)), _ll(x.numel()), _stream()), "relu2_rows")
+
+
+def softcap_rows(x: torch.Tensor, cap: float) -> None:
+    """x <- cap tanh(x / cap) in place; x float32."""
+    _need(x, "x", torch.float32)
+    _check(library("recurrent").cj_softcap_rows(_ptr(x), _f(cap), _ll(x.numel()), _stream()), "softcap_rows")
 
 
 # -- attention over a compressed latent ---------------------------------------------------------------

@@ -15,7 +15,13 @@
 //                      stores the step's last taps-1 inputs
 //   ssd_scan           S_t = exp(-A dt) S_(t-1) + dt B_t x_t^T ;  y_t = S_t^T C_t + D x_t
 //   delta_scan         S <- g S ; u = beta (v - S^T k) ; S <- S + k u^T ; o = S^T q
-//   gated_group_norm   y * silu(z) and RMS over equal parts of a row, in either order
+//   gla_scan           S_t = diag(alpha_t) S_(t-1) + k_t v_t^T ;  o_t = S_t^T q_t   (a decay per state row)
+//   mlstm_scan         m_t = max(f + m, i) ; S_t = e^(f + m - m_t) S + e^(i - m_t) k v^T ; n likewise with k alone ;
+//                      o = S^T q / (max(|n . q|, e^(-m_t)) + floor)
+//   rmsnorm_mix2       out (+)= c (a / rms(a) * wa + b / rms(b) * wb)
+//   relu2_rows         max(x, 0)^2 into the activation dtype
+//   softcap_rows       x <- cap tanh(x / cap), float32 in place (a head whose logits are capped)
+//   gated_group_norm   y * silu(z) (or sigmoid(z)) and RMS over equal parts of a row, in either order
 //
 // The two scans give a thread one column of the state (one value dimension) for a share of
 // its rows: a block is (request, head, tile of columns), a column's rows are dealt to DP
@@ -140,7 +146,13 @@ struct ScanArgs {
     float* out;          // [T, heads * cols]
     int heads, groups, rows, cols;           // rows: state rows (N or key dim); cols: value dim
     float q_scale;
+    float c0, c1;        // gla: c0 = 1 / tau ; mlstm: c0 = the gates' cap, c1 = the floor added to the read-out's divisor
 };
+
+constexpr int SCAN_SSD = 0, SCAN_DELTA = 1, SCAN_GLA = 2, SCAN_MLSTM = 3;
+
+// log(sigmoid(v)) without overflow on either side
+__device__ __forceinline__ float log_sigmoid_f(float v) { return fminf(v, 0.0f) - log1pf(expf(-fabsf(v))); }
 
 __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -170,8 +182,16 @@ __device__ __forceinline__ float lanes_sum(float v, int first) {
     return v;
 }
 
-template <int NPER, bool DELTA>
+// MODE 2 (gla) stages a third vector over the state's rows, the decays' inputs (from raw, columns off_dt +
+// head * rows), which the scalar phase turns into the decays alpha = sigmoid(z)^(1/tau) = exp(log_sigmoid(z) / tau).
+// MODE 3 (mlstm) keeps, beside a thread's share of its column, the same share of the vector n (every column of
+// a tile holds it: what a block reads at its start no other block writes) and the running maximum m:
+// a (slot, head, tile) holds [S: NPER x 128 | n: NPER x 128 | m: 128] floats.
+template <int NPER, int MODE>
 __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) {
+    constexpr bool DELTA = MODE == SCAN_DELTA;
+    constexpr int NVEC = MODE == SCAN_GLA ? 3 : 2;
+    constexpr int TILE_FLOATS = MODE == SCAN_MLSTM ? (2 * NPER + 1) * 128 : NPER * 128;
     cj::after_predecessor();
     cj::release_successor();
     extern __shared__ __align__(16) float staged[];
@@ -188,9 +208,9 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
     const bool live = col < p.cols;
     const int rows = p.rows, padded = DP * NPER;            // rows rounded up to what the lanes hold
     const int group = head / (p.heads / p.groups);
-    const int tail = 2 * padded + cols_blk;                 // where a staged token's four scalars begin
+    const int tail = NVEC * padded + cols_blk;              // where a staged token's four scalars begin
     const int stride = tail + 4;
-    float* S = p.state + (size_t)slot * p.slot_stride + ((size_t)head * gridDim.z + blockIdx.z) * NPER * 128;
+    float* S = p.state + (size_t)slot * p.slot_stride + ((size_t)head * gridDim.z + blockIdx.z) * TILE_FLOATS;
 
     // Where a staged token's entries come from is the same for every token: a thread works out, once,
     // the source of the entries it copies (entry e = thread + 128 k) as an offset into the token's row
@@ -198,19 +218,24 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
     constexpr int OWN = 4;                                  // entries a thread remembers; longer tokens take the general loop
     int own_off[OWN], own_kind[OWN];
     auto source = [&](int e, int& off) -> int {
-        if (e < 2 * padded) {
-            const int v = e < padded ? e : e - padded;      // index part * NPER + i  ->  row part + DP i
+        if (e < NVEC * padded) {
+            const int which = e / padded;
+            const int v = e - which * padded;               // index part * NPER + i  ->  row part + DP i
             const int d = (v / NPER) + DP * (v % NPER);
-            off = (e < padded ? p.off_a : p.off_b) + group * rows + d;
+            if (which == 2) {                               // gla: the decays' inputs, a row of raw per head
+                off = p.off_dt + head * rows + d;
+                return d < rows ? 2 : 0;
+            }
+            off = (which == 0 ? p.off_a : p.off_b) + group * rows + d;
             return d < rows ? 1 : 0;
         }
         if (e < tail) {
-            const int c = col0 + e - 2 * padded;
+            const int c = col0 + e - NVEC * padded;
             off = p.off_v + head * p.cols + c;
             return c < p.cols ? 1 : 0;
         }
-        if (e == tail) { off = p.off_dt + head; return 2; }
-        if (DELTA && e == tail + 1) { off = p.off_beta + head; return 2; }
+        if (MODE != SCAN_GLA && e == tail) { off = p.off_dt + head; return 2; }
+        if ((DELTA || MODE == SCAN_MLSTM) && e == tail + 1) { off = p.off_beta + head; return 2; }
         off = 0;
         return 0;
     };
@@ -248,9 +273,17 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
     float s[NPER];
 #pragma unroll
     for (int i = 0; i < NPER; ++i) s[i] = S[i * 128 + threadIdx.x];
-    const float A = expf(p.A_log[head]);
-    const float bias = p.dt_bias[head];
-    const float skip = DELTA ? 0.0f : p.skip[head];
+    // ssd, delta: A = exp(A_log), bias = the step size's; mlstm: A = the forget gate's bias, bias = the input gate's
+    const float A = MODE == SCAN_GLA ? 0.0f : (MODE == SCAN_MLSTM ? p.A_log[head] : expf(p.A_log[head]));
+    const float bias = MODE == SCAN_GLA ? 0.0f : p.dt_bias[head];
+    const float skip = MODE == SCAN_SSD ? p.skip[head] : 0.0f;
+    float nvec[MODE == SCAN_MLSTM ? NPER : 1];
+    float m_run = 0.0f;
+    if (MODE == SCAN_MLSTM) {
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) nvec[i] = S[(NPER + i) * 128 + threadIdx.x];
+        m_run = S[2 * NPER * 128 + threadIdx.x];
+    }
     float* out = p.out + (size_t)first * p.heads * p.cols + head * p.cols + col;
     const size_t out_ld = (size_t)p.heads * p.cols;
     const bool writer = live && part == 0;
@@ -281,6 +314,14 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
                     tk[tail + 2] = p.q_scale / sqrtf(qq + 1e-6f);         // q becomes a unit vector times q_scale
                     tk[tail + 3] = 1.0f / sqrtf(kk + 1e-6f);              // k a unit vector
                 }
+            } else if (MODE == SCAN_GLA) {
+                for (int d = lane; d < padded; d += 32) tk[2 * padded + d] = expf(log_sigmoid_f(tk[2 * padded + d]) * p.c0);
+            } else if (MODE == SCAN_MLSTM) {
+                if (lane == 0) {
+                    const float cap = p.c0;
+                    tk[tail] = cap * tanhf((tk[tail] + bias) / cap);                          // log of the input gate
+                    tk[tail + 1] = log_sigmoid_f(cap * tanhf((tk[tail + 1] + A) / cap));      // log of the forget gate
+                }
             } else if (lane == 0) {
                 const float dt = softplus_f(tk[tail] + bias);
                 tk[tail] = dt;
@@ -290,7 +331,7 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const float* tk = cur + tt * stride;
-            const float xv = tk[2 * padded + lcol];
+            const float xv = tk[NVEC * padded + lcol];
             float a[NPER], b[NPER];
             if (NPER % 4 == 0) {
 #pragma unroll
@@ -339,6 +380,43 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
                 }
                 y_prev = y;
                 t_prev = chunk * TOK + tt;
+            } else if (MODE == SCAN_GLA) {
+                // a = q, b = k, a row's decay from the third staged vector
+                float y = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    s[i] = fmaf(tk[2 * padded + part * NPER + i], s[i], b[i] * xv);
+                    y = fmaf(s[i], a[i] * p.q_scale, y);
+                }
+                y = lanes_sum(y, cols_per_warp);
+                if (writer) out[(size_t)(chunk * TOK + tt) * out_ld] = y;
+            } else if (MODE == SCAN_MLSTM) {
+                const float li = tk[tail], lf = tk[tail + 1];
+                const float m_new = fmaxf(lf + m_run, li);
+                const float keep = expf(lf + m_run - m_new), take = expf(li - m_new);
+                m_run = m_new;
+                float y = 0.0f, nq = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    const float kb = take * b[i], qa = a[i] * p.q_scale;
+                    s[i] = fmaf(keep, s[i], kb * xv);
+                    nvec[i] = fmaf(keep, nvec[i], kb);
+                    y = fmaf(s[i], qa, y);
+                    nq = fmaf(nvec[i], qa, nq);
+                }
+                if (cols_per_warp == 1) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        y += __shfl_xor_sync(0xffffffffu, y, o);
+                        nq += __shfl_xor_sync(0xffffffffu, nq, o);
+                    }
+                } else {
+                    for (int o = cols_per_warp; o < 32; o <<= 1) {
+                        y += __shfl_xor_sync(0xffffffffu, y, o);
+                        nq += __shfl_xor_sync(0xffffffffu, nq, o);
+                    }
+                }
+                if (writer) out[(size_t)(chunk * TOK + tt) * out_ld] = y / (fmaxf(fabsf(nq), expf(-m_run)) + p.c1);
             } else {
                 // a = B, b = C
                 const float dt = tk[tail], decay = tk[tail + 1];
@@ -361,12 +439,18 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
     }
 #pragma unroll
     for (int i = 0; i < NPER; ++i) S[i * 128 + threadIdx.x] = s[i];
+    if (MODE == SCAN_MLSTM) {
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) S[(NPER + i) * 128 + threadIdx.x] = nvec[i];
+        S[2 * NPER * 128 + threadIdx.x] = m_run;
+    }
 }
 
 // ---------------------------------------------------------------------------------
 // y * silu(z) and an RMS over equal parts of the row, in either order:
 //   gate_first:  v = y * silu(z);  out = v / rms_part(v) * w
 //   else:        out = y / rms_part(y) * w * silu(z)
+// (bit 0 of `gate_first` is the order; bit 1 set: the gate is sigmoid(z) instead of silu(z))
 // w has w_len entries and is indexed by (column % w_len): a weight per column of the row,
 // or one shared by all parts.  One warp per part.
 // ---------------------------------------------------------------------------------
@@ -379,26 +463,71 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int n, int 
     const int r = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int parts = n / part_len;
+    const bool plain_sigmoid = (gate_first & 2) != 0;
+    gate_first &= 1;
     for (int g = blockIdx.y * nw + warp; g < parts; g += gridDim.y * nw) {
         const float* yr = y + (size_t)r * n + (size_t)g * part_len;
         const float* zr = z + (size_t)r * ld_z + (size_t)g * part_len;
         float ss = 0.0f;
         for (int i = lane; i < part_len; i += 32) {
             float v = yr[i];
-            if (gate_first) { const float zz = zr[i]; v *= zz / (1.0f + expf(-zz)); }
+            if (gate_first) { const float zz = zr[i]; v *= (plain_sigmoid ? 1.0f : zz) / (1.0f + expf(-zz)); }
             ss = fmaf(v, v, ss);
         }
         ss = warp_sum(ss);
         const float scale = 1.0f / sqrtf(ss / (float)part_len + eps);
         for (int i = lane; i < part_len; i += 32) {
             const float zz = zr[i];
-            const float gate = zz / (1.0f + expf(-zz));
+            const float gate = (plain_sigmoid ? 1.0f : zz) / (1.0f + expf(-zz));
             const int c = g * part_len + i;
             float v = yr[i];
             v = gate_first ? (v * gate) * scale * w[c % w_len] : v * scale * w[c % w_len] * gate;
             out[(size_t)r * n + c] = from_f32<TO>(v);
         }
     }
+}
+
+// out (+)= c (a / rms(a) * wa + b / rms(b) * wb): the results of two mixers that read the same input, each
+// RMS-normed over the row with a weight of its own, averaged (c = 1/2) or summed.  A block a row.
+__global__ void rmsnorm_mix2_kernel(const float* __restrict__ a, const float* __restrict__ wa, const float* __restrict__ b,
+                                    const float* __restrict__ wb, float eps, float c, int accumulate, float* __restrict__ out, int H) {
+    cj::after_predecessor();
+    cj::release_successor();
+    __shared__ float scratch[32];
+    const float* ra = a + (size_t)blockIdx.x * H;
+    const float* rb = b + (size_t)blockIdx.x * H;
+    float* dst = out + (size_t)blockIdx.x * H;
+    float sa = 0.0f, sb = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        sa = fmaf(ra[i], ra[i], sa);
+        sb = fmaf(rb[i], rb[i], sb);
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float fa = 1.0f / sqrtf(sa / (float)H + eps), fb = 1.0f / sqrtf(sb / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = c * (ra[i] * fa * wa[i] + rb[i] * fb * wb[i]);
+        dst[i] = accumulate ? dst[i] + v : v;
+    }
+}
+
+// max(x, 0)^2 into the activation dtype (the activation of an ungated expert whose product was stored in float32)
+template <typename TO>
+__global__ void relu2_rows_kernel(const float* __restrict__ x, TO* __restrict__ out, long long n) {
+    cj::after_predecessor();
+    cj::release_successor();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = fmaxf(x[i], 0.0f);
+        out[i] = from_f32<TO>(v * v);
+    }
+}
+
+// x <- cap tanh(x / cap), in place, float32
+__global__ void softcap_rows_kernel(float* __restrict__ x, float cap, long long n) {
+    cj::after_predecessor();
+    cj::release_successor();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
 }
 
 }  // namespace
@@ -475,14 +604,25 @@ CJ_EXPORT int cj_short_conv_commit(const float* in, int ld_in, int C, int taps, 
 }
 
 // mode 0: the state-space scan (off_a = B, off_b = C, off_v = x; off_dt in raw);
-// mode 1: the gated delta rule (off_a = q, off_b = k, off_v = v; off_dt = decay input, off_beta in raw).
+// mode 1: the gated delta rule (off_a = q, off_b = k, off_v = v; off_dt = decay input, off_beta in raw);
+// mode 2: gated linear attention (off_a = q, off_b = k, off_v = v; raw columns off_dt + head * rows + d = the decays'
+//         inputs; c0 = 1 / tau; A_log, dt_bias unused);
+// mode 3: the matrix memory with exponential gating (off_a = q, off_b = k, off_v = v; raw columns off_dt + head = the
+//         input gate's, off_beta + head = the forget gate's pre-activation; dt_bias = the input gate's bias, A_log = the
+//         forget gate's; c0 = the gates' cap, c1 = the floor added to the read-out's divisor).
+static long long scan_tile_floats(int mode, int nper) { return mode == 3 ? (long long)(2 * nper + 1) * 128 : (long long)nper * 128; }
+
 CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off_b, int off_v, const float* raw, int ld_raw,
                             int off_dt, int off_beta, const float* A_log, const float* dt_bias, const float* skip, float* state,
                             long long slot_stride, long long state_floats, const int* req_start, const int* req_slot, float* out,
-                            int requests, int heads, int groups, int rows, int cols, float q_scale, cudaStream_t stream) {
+                            int requests, int heads, int groups, int rows, int cols, float q_scale, float c0, float c1,
+                            cudaStream_t stream) {
     if (requests <= 0) return 0;
-    if (!x || !raw || !A_log || !dt_bias || !state || !req_start || !req_slot || !out) return CJ_ERR_ARG;
+    if (mode < 0 || mode > 3) return CJ_ERR_ARG;
+    if (!x || !raw || !state || !req_start || !req_slot || !out) return CJ_ERR_ARG;
+    if (mode != 2 && (!A_log || !dt_bias)) return CJ_ERR_ARG;
     if (mode == 0 && !skip) return CJ_ERR_ARG;
+    if ((mode == 2 || mode == 3) && !(c0 > 0.0f)) return CJ_ERR_ARG;
     if (heads <= 0 || groups <= 0 || heads % groups != 0 || rows <= 0 || cols <= 0) return CJ_ERR_SIZE;
     const int DP = scan_lanes(heads, rows, cols);
     const int per = (rows + DP - 1) / DP;
@@ -490,27 +630,32 @@ CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off
     int nper = 1;
     while (nper < per) nper <<= 1;
     ScanArgs p{x, ld, off_a, off_b, off_v, raw, ld_raw, off_dt, off_beta, A_log, dt_bias, skip, state, slot_stride,
-               req_start, req_slot, out, heads, groups, rows, cols, q_scale};
+               req_start, req_slot, out, heads, groups, rows, cols, q_scale, c0, c1};
     const int cols_per_block = 4 * (32 / DP);
     dim3 grid(requests, heads, (cols + cols_per_block - 1) / cols_per_block);
     if (grid.y > 65535 || grid.z > 65535) return CJ_ERR_SIZE;
-    if (state_floats < (long long)heads * grid.z * nper * 128) return CJ_ERR_SIZE;
+    if (state_floats < (long long)heads * grid.z * scan_tile_floats(mode, nper)) return CJ_ERR_SIZE;
     // tokens staged at a time: up to 16, as many as 96 KB of shared memory hold twice
-    const size_t token_bytes = (size_t)(2 * DP * nper + cols_per_block + 4) * sizeof(float);
+    const size_t token_bytes = (size_t)((mode == 2 ? 3 : 2) * DP * nper + cols_per_block + 4) * sizeof(float);
     int TOK = (int)((96 * 1024) / (2 * token_bytes));
     if (TOK > 16) TOK = 16;
     if (TOK < 1) return CJ_ERR_SIZE;
     const size_t smem = 2 * (size_t)TOK * token_bytes;
-#define LAUNCH(N)                                                                                                       \
+#define LAUNCH_MODE(N, M)                                                                                               \
     do {                                                                                                                \
         static bool sized = false;                                                                                      \
         if (!sized) {                                                                                                   \
-            cudaFuncSetAttribute(scan_kernel<N, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);        \
-            cudaFuncSetAttribute(scan_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);         \
+            cudaFuncSetAttribute(scan_kernel<N, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);            \
             sized = true;                                                                                               \
         }                                                                                                               \
-        if (mode == 0) cj::launch(scan_kernel<N, false>, grid, dim3(128), smem, stream, p, DP, TOK);                    \
-        else cj::launch(scan_kernel<N, true>, grid, dim3(128), smem, stream, p, DP, TOK);                               \
+        cj::launch(scan_kernel<N, M>, grid, dim3(128), smem, stream, p, DP, TOK);                                       \
+    } while (0)
+#define LAUNCH(N)                                                                                                       \
+    do {                                                                                                                \
+        if (mode == 0) LAUNCH_MODE(N, SCAN_SSD);                                                                        \
+        else if (mode == 1) LAUNCH_MODE(N, SCAN_DELTA);                                                                 \
+        else if (mode == 2) LAUNCH_MODE(N, SCAN_GLA);                                                                   \
+        else LAUNCH_MODE(N, SCAN_MLSTM);                                                                                \
     } while (0)
     switch (nper) {
         case 1: LAUNCH(1); break;
@@ -522,22 +667,27 @@ CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off
         default: LAUNCH(64);
     }
 #undef LAUNCH
+#undef LAUNCH_MODE
     return launch_status();
 }
 
 // floats of state one (slot, schedule entry) needs for heads matrices of rows x cols in the scan's own layout
-CJ_EXPORT long long cj_state_scan_floats(int heads, int rows, int cols) {
+// (mode 3 keeps a vector over the rows and a scalar beside every tile of a matrix)
+CJ_EXPORT long long cj_state_scan_floats_mode(int mode, int heads, int rows, int cols) {
     if (heads <= 0 || rows <= 0 || cols <= 0) return 0;
     const int DP = scan_lanes(heads, rows, cols);
     const int per = (rows + DP - 1) / DP;
     int nper = 1;
     while (nper < per) nper <<= 1;
     const int cols_per_block = 4 * (32 / DP);
-    return (long long)heads * ((cols + cols_per_block - 1) / cols_per_block) * nper * 128;
+    return (long long)heads * ((cols + cols_per_block - 1) / cols_per_block) * scan_tile_floats(mode, nper);
 }
+
+CJ_EXPORT long long cj_state_scan_floats(int heads, int rows, int cols) { return cj_state_scan_floats_mode(0, heads, rows, cols); }
 
 CJ_EXPORT int cj_gated_group_norm(const float* y, int n, int part_len, const float* z, int ld_z, const float* w, int w_len,
                                   float eps, int gate_first, void* out, int out_dtype, int rows, cudaStream_t stream) {
+    // gate_first: bit 0 the gate multiplies before the norm's statistics, bit 1 the gate is sigmoid(z), not silu(z)
     if (rows <= 0) return 0;
     if (!y || !z || !w || !out || n <= 0 || part_len <= 0 || w_len <= 0) return CJ_ERR_ARG;
     if (n % part_len != 0) return CJ_ERR_SIZE;
@@ -549,5 +699,34 @@ CJ_EXPORT int cj_gated_group_norm(const float* y, int n, int part_len, const flo
     if (out_dtype == CJ_F32) cj::launch(gated_group_norm_kernel<float>, grid, dim3(warps * 32), 0, stream, y, n, part_len, z, ld_z, w, w_len, eps, gate_first, (float*)out);
     else if (out_dtype == CJ_BF16) cj::launch(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(warps * 32), 0, stream, y, n, part_len, z, ld_z, w, w_len, eps, gate_first, (__nv_bfloat16*)out);
     else return CJ_ERR_DTYPE;
+    return launch_status();
+}
+
+CJ_EXPORT int cj_rmsnorm_mix2(const float* a, const float* wa, const float* b, const float* wb, float eps, float c, int accumulate,
+                              float* out, int rows, int H, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!a || !wa || !b || !wb || !out || H <= 0) return CJ_ERR_ARG;
+    int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    cj::launch(rmsnorm_mix2_kernel, dim3(rows), dim3(threads), 0, stream, a, wa, b, wb, eps, c, accumulate, out, H);
+    return launch_status();
+}
+
+CJ_EXPORT int cj_relu2_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!x || !out) return CJ_ERR_ARG;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_dtype == CJ_F32) cj::launch(relu2_rows_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, x, (float*)out, n);
+    else if (out_dtype == CJ_BF16) cj::launch(relu2_rows_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, x, (__nv_bfloat16*)out, n);
+    else return CJ_ERR_DTYPE;
+    return launch_status();
+}
+
+CJ_EXPORT int cj_softcap_rows(float* x, float cap, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!x || !(cap > 0.0f)) return CJ_ERR_ARG;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cj::launch(softcap_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, cap, n);
     return launch_status();
 }

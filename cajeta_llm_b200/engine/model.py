@@ -74,7 +74,9 @@ class Model:
         return [self.blocks[e.layer].mixer.cache_need() for e in self.plan.schedule]
 
     def state_needs(self) -> List[Optional[StateNeed]]:
-        return [self.blocks[e.layer].mixer.state_need() for e in self.plan.schedule]
+        """A block that keeps state of its own beside its mixer's (``state_need`` on the block) answers for the entry."""
+        return [(getattr(self.blocks[e.layer], "state_need", None) or self.blocks[e.layer].mixer.state_need)()
+                for e in self.plan.schedule]
 
     def cache_from(self) -> List[Optional[int]]:
         return [e.cache_from for e in self.plan.schedule]

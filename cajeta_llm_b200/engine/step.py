@@ -56,6 +56,7 @@ class EntryContext:
     block_table: Optional[torch.Tensor]      # int32 [requests, width] of the entry's group
     page_tokens: int
     state: Optional[torch.Tensor]            # [max_seqs, ...] per-request state of this entry
+    state_offset: int = 0                    # where, in a request's flat state vector, the part being run finds its share
 
 
 @dataclass
@@ -152,6 +153,8 @@ class ModelRunner:
         # requests a step's layout is filled up with (slot -1, no rows).
         mixers = [model.blocks[e.layer].mixer for e in model.plan.schedule]
         graph_safe = all(getattr(m, "graph_safe", m.state_need() is None) for m in mixers)
+        # a block that keeps state of its own (in front of its mixer's) answers for both
+        graph_safe = graph_safe and all(getattr(model.blocks[e.layer], "graph_safe", True) for e in model.plan.schedule)
         self.cuda_graphs = cuda_graphs and graph_safe and self.runtime.fast_kernels and self.runtime.device.type == "cuda"
         # a mixer may run steps of many rows in a form that reads the requests' lengths on the host
         # (``capture_max_rows``): steps with more rows than that are launched kernel by kernel

@@ -26,6 +26,20 @@ is also the value;
 ``names``: the tensor names of ``q``, ``k``, ``v``, ``o`` under the part's prefix.
 A position part's ``magnitude`` (a stretched rotation's) multiplies cos and sin.
 
+Further optional parameters; a mixer that sets any of them runs ``head_prepare`` and the attention kernel that
+sees all heads of a row at once (``mixed_heads_attention``):
+``proj_conv``: ``{"taps": n, "q": name, "k": name, "v": name}``, a causal convolution over time on every channel
+of q, k and v right after the projection (``y_t = sum_j w[:, j] u_(t - taps + 1 + j)``, weights ``[channels, taps]``,
+no bias, no activation); the last ``taps - 1`` projected rows of a request are per-request state
+(``state_need()``), found at ``entry.state_offset`` of the entry's state;
+``qk_norm`` with ``"whole": true``: ONE statistic over all heads of q (of k), weights of ``heads * head_dim``
+(``kv_heads * head_dim``) entries;
+``head_temp``: a tensor name, ``[heads]``: head h's score is multiplied by its entry (after the scale);
+``talk``: a tensor name, ``[heads, heads]``: the heads' scores of a (query, key) pair are mixed before the
+softmax, ``s_h <- sum_g talk[h, g] s_g``;
+``sink``: a tensor name, ``[heads]``: the softmax's divisor also holds ``exp(sink[h])``, a key without value
+that is neither scaled nor mixed.
+
 An entry that reads another entry's cache (``entry.writes_cache`` false) projects and
 rotates only q.
 """
@@ -60,6 +74,10 @@ class PagedAttention(Part):
         self.qk_norm = dict(spec.get("qk_norm") or {}) or None
         self.values_from_keys = bool(spec.get("values_from_keys", False))
         self.head_gate = spec.get("head_gate") or None
+        self.proj_conv = dict(spec.get("proj_conv") or {}) or None
+        self.head_temp = spec.get("head_temp") or None
+        self.talk = spec.get("talk") or None
+        self.sink = spec.get("sink") or None
         names = dict(spec.get("names") or {})
         self.n_proj = {n: self.name(names.get(n, f"{n}_proj.weight")) for n in ("q", "k", "v", "o")}
         self.allow_pending = True          # a block that has no norm after the mixer sets this False
@@ -78,8 +96,18 @@ class PagedAttention(Part):
         self.o_dim = self.heads * self.value_dim
         self.general = bool(self.softcap > 0.0 or self.qk_norm or self.values_from_keys or self.head_gate
                             or self.value_dim != self.head_dim or getattr(self.position, "magnitude", 1.0) != 1.0)
+        self.norm_whole = bool(self.qk_norm and self.qk_norm.get("whole"))
+        self.mixed = bool(self.proj_conv or self.head_temp or self.talk or self.sink or self.norm_whole)
+        self.general = self.general or self.mixed
         if self.general and (self.qkv_bias or self.out_bias):
             raise ValueError("the general attention path is built without biases")
+        if self.mixed and (self.softcap > 0.0 or self.head_gate or self.values_from_keys):
+            raise ValueError("mixed heads, a sink or a convolved projection are built without softcap, head_gate and values_from_keys")
+        self.taps = int(self.proj_conv["taps"]) if self.proj_conv else 1
+        if self.taps < 1:
+            raise ValueError(f"proj_conv.taps must be >= 1, found {self.taps}")
+        self.graph_safe = True             # rows, requests and slots come from the step's device metadata only
+        self.w_conv = self.temp_w = self.talk_w = self.sink_w = None
         self.q_norm_w = self.k_norm_w = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.b_qkv: Optional[torch.Tensor] = None
@@ -91,6 +119,9 @@ class PagedAttention(Part):
         return KvNeed(self.kv_heads, self.head_dim, self.window, value_dim=0 if self.value_dim == self.head_dim else self.value_dim)
 
     def state_need(self):
+        if self.proj_conv and self.taps > 1:
+            from .base import StateNeed
+            return StateNeed(((self.taps - 1) * (self.q_dim + self.kv_dim + self.v_dim),), torch.float32)
         return None
 
     # -- tensors ---------------------------------------------------------------------
@@ -103,8 +134,17 @@ class PagedAttention(Part):
         if not self.values_from_keys:
             p[self.n_proj["v"]] = ParamSpec((self.v_dim, self.hidden))
         if self.qk_norm:
-            p[self.name(self.qk_norm["q"])] = ParamSpec((self.head_dim,), role="vector", init="ones")
-            p[self.name(self.qk_norm["k"])] = ParamSpec((self.head_dim,), role="vector", init="ones")
+            p[self.name(self.qk_norm["q"])] = ParamSpec((self.q_dim if self.norm_whole else self.head_dim,), role="vector", init="ones")
+            p[self.name(self.qk_norm["k"])] = ParamSpec((self.kv_dim if self.norm_whole else self.head_dim,), role="vector", init="ones")
+        if self.proj_conv:
+            for n, rows in (("q", self.q_dim), ("k", self.kv_dim), ("v", self.v_dim)):
+                p[self.name(self.proj_conv[n])] = ParamSpec((rows, self.taps), role="vector", std=0.2)
+        if self.head_temp:
+            p[self.name(self.head_temp)] = ParamSpec((self.heads,), role="vector", init="ones")
+        if self.talk:
+            p[self.name(self.talk)] = ParamSpec((self.heads, self.heads), role="vector", std=0.3)
+        if self.sink:
+            p[self.name(self.sink)] = ParamSpec((self.heads,), role="vector", std=1.0)
         if self.head_gate:
             p[self.name(self.head_gate)] = ParamSpec((self.heads, self.hidden))
         if self.qkv_bias:
@@ -117,7 +157,9 @@ class PagedAttention(Part):
 
     def libraries(self) -> set:
         libs = {"rowwise", "gemm_simt"}
-        if self.general:
+        if self.mixed:
+            libs |= {"attention_paged"} | ({"recurrent"} if self.proj_conv else set())
+        elif self.general:
             libs.add("attention_paged")
             if self.runtime.fast_kernels and self.value_dim == self.head_dim:
                 if self.head_dim in (64, 128):
@@ -141,6 +183,11 @@ class PagedAttention(Part):
         if self.qk_norm:
             self.q_norm_w = self.fetch(source, self.name(self.qk_norm["q"]))
             self.k_norm_w = self.fetch(source, self.name(self.qk_norm["k"]))
+        if self.proj_conv:
+            self.w_conv = torch.cat([self.fetch(source, self.name(self.proj_conv[n])) for n in ("q", "k", "v")], dim=0).contiguous()
+        for attr, n in (("temp_w", self.head_temp), ("talk_w", self.talk), ("sink_w", self.sink)):
+            if n:
+                setattr(self, attr, self.fetch(source, self.name(n)))
         if self.qkv_bias:
             self.b_qkv = torch.cat([self.fetch(source, self.name(f"{n}_proj.bias")) for n in ("q", "k", "v")], dim=0).contiguous()
         self.w_o = self.fetch(source, self.n_proj["o"])
@@ -149,6 +196,8 @@ class PagedAttention(Part):
 
     # -- one step --------------------------------------------------------------------
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, entry) -> Optional[torch.Tensor]:
+        if self.mixed:
+            return self._forward_mixed(x, residual, ctx, entry)
         if self.general:
             return self._forward_general(x, residual, ctx, entry)
         rt = self.runtime
@@ -243,3 +292,41 @@ class PagedAttention(Part):
             project(rt, out.view(T, self.o_dim), self.w_o, residual, accumulate=True)
         K.tag = None
         return parts
+
+    def _forward_mixed(self, x: torch.Tensor, residual: torch.Tensor, ctx, entry) -> None:
+        """The path of a mixer whose projections are convolved over time, whose norm spans all heads, or whose heads'
+        scores are scaled, mixed or joined by a sink: one product for q | k | v, the convolution with its state, heads made
+        ready (norm, rotation, cache write), attention over all heads of a row at once, output projection."""
+        rt = self.runtime
+        T = x.shape[0]
+        pos = self.position
+        if not entry.writes_cache:
+            raise ValueError("an attention mixer with mixed heads owns its cache (cache_from is not built for it)")
+        k_off, v_off = self.q_dim, self.q_dim + self.kv_dim
+        C = v_off + self.v_dim
+        qkv = torch.empty((T, C), dtype=torch.float32, device=x.device)
+        K.tag = "qkv"
+        project(rt, x, self.w_qkv, qkv)
+        if self.proj_conv:
+            at = getattr(entry, "state_offset", 0)
+            conv = torch.empty((T, C), dtype=torch.float32, device=x.device)
+            K.tag = "short conv"
+            K.short_conv(qkv, 0, C, self.taps, self.w_conv, None, entry.state, ctx.row_req, ctx.req_start, ctx.req_slot, conv,
+                         activate=False, state_offset=at)
+            K.short_conv_commit(qkv, 0, C, self.taps, entry.state, ctx.req_start, ctx.req_slot, ctx.n_requests, state_offset=at)
+            qkv = conv
+        q = torch.empty((T, self.heads, self.head_dim), dtype=rt.act_dtype, device=x.device)
+        K.tag = "heads + cache write"
+        K.head_prepare(qkv, 0, k_off, v_off, q, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
+                       entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.value_dim, pos.rotary_dim, pos.inv_freq,
+                       getattr(pos, "magnitude", 1.0), self.q_norm_w, self.k_norm_w,
+                       float(self.qk_norm["eps"]) if self.qk_norm else 0.0, True, norm_whole=self.norm_whole)
+        out = torch.empty((T, self.heads, self.value_dim), dtype=rt.act_dtype, device=x.device)
+        K.tag = "attention"
+        K.mixed_heads_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
+                                entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.value_dim, self.window,
+                                self.scale, temp=self.temp_w, talk=self.talk_w, sink=self.sink_w)
+        K.tag = "o"
+        project(rt, out.view(T, self.o_dim), self.w_o, residual, accumulate=True)
+        K.tag = None
+        return None

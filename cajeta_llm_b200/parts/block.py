@@ -17,15 +17,27 @@ kernel norms and adds.  Same parameters as ``prenorm``.
 (each adds its result into the float32 stream).  A layer may have no feed-forward.  After the
 sublayers the layer's ``stream_after`` part, when it has one, runs on the stream.  Parameters:
 ``mixer_norm_name``, ``mixer_name``, ``feed_forward_name``, ``stream_after_name``.
+
+``sandwich``: a norm before AND after each sublayer: ``hs += norm_1b(mixer(c(norm_1(hs))))``,
+``hs += norm_2b(feed_forward(norm_2(hs)))``; a layer may have no feed-forward.  ``c`` is an optional causal
+convolution over time on the mixer's input (``input_conv``: ``{"taps": n, "name": tensor}``):
+``c(h)_t = h_t + sum_j w[:, j] h_(t - taps + 1 + j)`` per channel, zeros before the sequence's start, weights
+``[hidden, taps]``; it runs in float32 on the float32 normed row, and the last ``taps - 1`` normed rows of a
+request are per-request state.  The block therefore declares state itself (``state_need()``): the
+convolution's share first, then the mixer's, which the mixer finds at ``entry.state_offset``.  Parameters:
+``mixer_norm_name``, ``mixer_post_norm_name``, ``feed_forward_norm_name``, ``feed_forward_post_norm_name``,
+``mixer_name``, ``feed_forward_name``, ``input_conv``, ``hidden_size``.  The post norms are the layer's norm
+specs (``mixer_norm`` / ``feed_forward_norm``) under their own names.
 """
 from __future__ import annotations
 
-from typing import Dict
+from dataclasses import replace
+from typing import Dict, Optional
 
 import torch
 
 from ..csrc import kernels as K
-from .base import Part, make_part, register_part
+from .base import Part, StateNeed, make_part, register_part
 from .plan import LayerSpec, ParamSpec
 
 
@@ -181,3 +193,106 @@ class ParallelBlock(Part):
             ff.forward(x, x_exact, hs, ctx)
         if self.after is not None:
             self.after.forward(hs, ctx)
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Part):
+    def __init__(self, spec, prefix, runtime, layer: LayerSpec):
+        super().__init__(spec, prefix, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.mixer_norm = make_part("norm", layer.mixer_norm, self.name(spec["mixer_norm_name"]), runtime)
+        self.mixer_post_norm = make_part("norm", layer.mixer_norm, self.name(spec["mixer_post_norm_name"]), runtime)
+        self.mixer = make_part("mixer", layer.mixer, self.name(spec["mixer_name"]), runtime)
+        if hasattr(self.mixer, "allow_pending"):
+            self.mixer.allow_pending = False       # the mixer's result is normed before it is added: no partial sums
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = make_part("norm", layer.feed_forward_norm, self.name(spec["feed_forward_norm_name"]), runtime)
+            self.feed_forward_post_norm = make_part("norm", layer.feed_forward_norm, self.name(spec["feed_forward_post_norm_name"]), runtime)
+            self.feed_forward = make_part("feed_forward", layer.feed_forward, self.name(spec["feed_forward_name"]), runtime)
+        for n in (self.mixer_post_norm, self.feed_forward_post_norm):
+            if n is not None and not (hasattr(n, "weight") and hasattr(n, "eps")):
+                raise ValueError("a sandwich block takes post norms that are a weight and an eps (rmsnorm)")
+        conv = dict(spec.get("input_conv") or {})
+        self.taps = int(conv.get("taps", 1)) if conv else 1
+        self.conv_name = self.name(conv["name"]) if conv else None
+        if self.taps < 1:
+            raise ValueError(f"input_conv.taps must be >= 1, found {self.taps}")
+        self.conv_state = (self.taps - 1) * self.hidden if conv else 0
+        self.w_conv = None
+        self.graph_safe = getattr(self.mixer, "graph_safe", self.mixer.state_need() is None)
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.feed_forward_norm, self.feed_forward,
+                                 self.feed_forward_post_norm) if p is not None)
+
+    def state_need(self) -> Optional[StateNeed]:
+        need = self.mixer.state_need()
+        if need is None:
+            return StateNeed((self.conv_state,), torch.float32) if self.conv_state else None
+        if not self.conv_state:
+            return need
+        if need.dtype != torch.float32 or len(need.shape) != 1:
+            raise ValueError("sandwich: behind an input convolution the mixer's state must be a flat float32 vector")
+        return StateNeed((self.conv_state + int(need.shape[0]),), torch.float32)
+
+    def params(self) -> Dict[str, ParamSpec]:
+        out: Dict[str, ParamSpec] = {}
+        for p in self.parts():
+            out.update(p.params())
+        if self.conv_name:
+            out[self.conv_name] = ParamSpec((self.hidden, self.taps), role="vector", std=0.2)
+        return out
+
+    def libraries(self) -> set:
+        out = {"recurrent"}
+        for p in self.parts():
+            out |= p.libraries()
+        return out
+
+    def load(self, source) -> None:
+        for p in self.parts():
+            p.load(source)
+        if self.conv_name:
+            # h + conv(h) as ONE convolution: the newest tap's weight plus one (exact in float32 for weights that
+            # came from 16-bit storage; else the sum rounds once, as h + w h would)
+            w = self.fetch(source, self.conv_name).clone()
+            w[:, self.taps - 1] += 1.0
+            self.w_conv = w.contiguous()
+
+    def _mixer_input(self, hs: torch.Tensor, ctx, entry) -> torch.Tensor:
+        rt = self.runtime
+        if not self.conv_name:
+            x, _ = self.mixer_norm.forward(hs)
+            return x
+        h, _ = self.mixer_norm.forward(hs, out_dtype=torch.float32)
+        x = torch.empty(h.shape, dtype=rt.act_dtype, device=hs.device)
+        K.tag = "input conv"
+        K.short_conv(h, 0, self.hidden, self.taps, self.w_conv, None, entry.state, ctx.row_req, ctx.req_start, ctx.req_slot, x,
+                     activate=False, state_offset=entry.state_offset)
+        K.short_conv_commit(h, 0, self.hidden, self.taps, entry.state, ctx.req_start, ctx.req_slot, ctx.n_requests,
+                            state_offset=entry.state_offset)
+        K.tag = None
+        return x
+
+    def forward(self, hs: torch.Tensor, ctx, entry) -> None:
+        x = self._mixer_input(hs, ctx, entry)
+        y = torch.zeros_like(hs)
+        inner = replace(entry, state_offset=entry.state_offset + self.conv_state) if self.conv_state else entry
+        pending = self.mixer.forward(x, y, ctx, inner)
+        if pending is not None:
+            y += pending.sum(dim=0)
+        K.tag = "norm + add"
+        K.rmsnorm_add(hs, y, self.mixer_post_norm.weight, self.mixer_post_norm.eps)
+        K.tag = None
+        ff = self.feed_forward
+        if ff is None:
+            return
+        wants_split = getattr(ff, "wants_split_input", None)
+        split = bool(wants_split and wants_split(hs.shape[0]))
+        x, x_exact = self.feed_forward_norm.forward(hs, want_f32=getattr(ff, "needs_f32_input", False) and not split, want_split=split)
+        y = torch.zeros_like(hs)
+        ff.forward(x, x_exact, y, ctx)
+        K.tag = "norm + add"
+        K.rmsnorm_add(hs, y, self.feed_forward_post_norm.weight, self.feed_forward_post_norm.eps)
+        K.tag = None

@@ -3,7 +3,8 @@
 ``token_embedding`` (category ``embedding``): ``hs[t, :] = W[token_t, :]`` widened to the
 float32 residual stream, times ``scale`` when one is given (the reference's
 ``embedScale``, 0 = none: model/Embedding.cajeta:73-81, model/HostOps.cajeta:32-49).
-Parameters: ``scale`` (optional).  Must offer ``forward(token_ids int32 [T]) -> float32
+Parameters: ``scale`` (optional); ``norm`` (optional: ``{"eps": e, "weight_name": tensor}``, an RMS norm with a
+plain weight over every embedded row, in float32).  Must offer ``forward(token_ids int32 [T]) -> float32
 [T, hidden]`` and ``table`` (the ``[vocab, hidden]`` tensor, which a tied head reads).
 
 ``pair_hash_embedding`` (category ``embedding``): the token's row plus a row of a second table chosen by
@@ -17,7 +18,8 @@ step's device metadata only.  Parameters: ``buckets``, ``mul_prev``, ``mul_cur``
 given (the final norm has already picked and normed the wanted rows:
 model/CausalLM.cajeta:1712-1718); ``W`` is the embedding table when the plan names no
 head tensor (model/CausalLM.cajeta:625-631).  Parameters: ``bias`` (optional, default
-false; its tensor is the head's name with ``weight`` replaced by ``bias``).  Must offer
+false; its tensor is the head's name with ``weight`` replaced by ``bias``), ``softcap`` c > 0 (optional: the
+logits become ``c tanh(logits / c)``, in float32).  Must offer
 ``forward(x [rows, hidden]) -> float32 [rows, vocab]``.
 
 Both are built by the model with the plan's sizes and tensor names as keyword arguments
@@ -46,20 +48,33 @@ class TokenEmbedding(Part):
         self.weight_name = weight_name
         self.scale = float(spec.get("scale", 0.0) or 0.0)
         self.table: Optional[torch.Tensor] = None
+        norm = dict(spec.get("norm") or {})
+        self.norm_eps = float(norm["eps"]) if norm else 0.0
+        self.norm_name = str(norm["weight_name"]) if norm else None
+        self.norm_weight: Optional[torch.Tensor] = None
 
     def params(self) -> Dict[str, ParamSpec]:
-        return {self.weight_name: ParamSpec((self.vocab, self.hidden))}
+        p = {self.weight_name: ParamSpec((self.vocab, self.hidden))}
+        if self.norm_name:
+            p[self.norm_name] = ParamSpec((self.hidden,), role="vector", init="ones")
+        return p
 
     def libraries(self) -> set:
         return {"rowwise"}
 
     def load(self, source) -> None:
         self.table = self.fetch(source, self.weight_name)
+        if self.norm_name:
+            self.norm_weight = self.fetch(source, self.norm_name)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         hs = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
         K.tag = "embedding"
         K.embed_gather(hs, self.table, token_ids, self.scale)
+        if self.norm_name:
+            normed = torch.empty_like(hs)
+            K.rmsnorm(hs, self.norm_weight, self.norm_eps, normed)
+            hs = normed
         K.tag = None
         return hs
 
@@ -112,6 +127,9 @@ class LinearHead(Part):
         self.weight_name = weight_name               # None: tied to the embedding table
         self.embedding = embedding
         self.has_bias = bool(spec.get("bias", False))
+        self.softcap = float(spec.get("softcap", 0.0) or 0.0)
+        if self.softcap < 0.0:
+            raise ValueError(f"softcap must be positive (or 0 for none), found {self.softcap}")
         if self.has_bias and weight_name is None:
             raise ValueError("a head tied to the embedding table has no tensor name to derive its bias from")
         self.bias_name = weight_name[: -len("weight")] + "bias" if self.has_bias and weight_name.endswith("weight") else (
@@ -128,7 +146,7 @@ class LinearHead(Part):
         return out
 
     def libraries(self) -> set:
-        libs = {"gemm_simt"}
+        libs = {"gemm_simt"} | ({"recurrent"} if self.softcap else set())
         if self.runtime.fast_kernels and self.hidden >= 128:
             libs.add("gemm_tc")
         return libs
@@ -142,5 +160,7 @@ class LinearHead(Part):
         out = torch.empty((x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
         K.tag = "head"
         project(self.runtime, x, self.weight, out, bias=self.bias)
+        if self.softcap:
+            K.softcap_rows(out, self.softcap)
         K.tag = None
         return out

@@ -31,7 +31,9 @@ the weight multiplying the float32 row before it is rounded for the products);
 ``u = clamp(W_u x, -L, L)``, ``W_d (g sigmoid(a g) (u + 1))`` instead of SwiGLU; ``shared_act_limit`` /
 ``shared_act_alpha``: the same for the shared expert (default: the experts');
 ``route_groups`` ``(count, keep)``: the experts form ``count`` equal groups of neighbours, a group's
-score is its largest score, and only experts of the ``keep`` best groups can be picked.
+score is its largest score, and only experts of the ``keep`` best groups can be picked;
+``activation`` ``relu2``: an expert has no gate, ``W_d max(W_u x, 0)^2`` (tensors ``up`` and ``down`` only;
+built without a shared expert and with the weight on the output).
 
 The file stores one tensor per expert and projection
 (``experts.{e}.gate_proj.weight`` ...); they are stacked into ``[E, I, H]`` and
@@ -116,6 +118,12 @@ class SparseMoE(Part):
         self.act_alpha = float(spec.get("act_alpha", 1.0))
         self.shared_act_limit = float(spec.get("shared_act_limit", self.act_limit) or 0.0)
         self.shared_act_alpha = float(spec.get("shared_act_alpha", self.act_alpha))
+        self.activation = str(spec.get("activation", "swiglu"))
+        if self.activation not in ("swiglu", "relu2"):
+            raise ValueError(f"activation must be 'swiglu' or 'relu2', found '{self.activation}'")
+        self.gated = self.activation == "swiglu"
+        if not self.gated and (self.shared_inter > 0 or self.weight_on != "output" or self.act_limit > 0.0):
+            raise ValueError("ungated experts are built without a shared expert, capped gates or the weight on the input")
         groups = spec.get("route_groups")
         self.route_groups = (int(groups[0]), int(groups[1])) if groups and int(groups[0]) > 1 else None
         if self.route_groups:
@@ -146,7 +154,8 @@ class SparseMoE(Part):
     def params(self) -> Dict[str, ParamSpec]:
         p = {self.n_router: ParamSpec((self.num_experts, self.hidden), role="vector")}
         for e in range(self.num_experts):
-            p[self.expert_name("gate", e)] = ParamSpec((self.inter, self.hidden))
+            if self.gated:
+                p[self.expert_name("gate", e)] = ParamSpec((self.inter, self.hidden))
             p[self.expert_name("up", e)] = ParamSpec((self.inter, self.hidden))
             p[self.expert_name("down", e)] = ParamSpec((self.hidden, self.inter))
         if self.shared_inter > 0:
@@ -161,7 +170,7 @@ class SparseMoE(Part):
         return self.name(self.n_expert[proj].format(e=e))
 
     def libraries(self) -> set:
-        libs = {"rowwise", "moe_route", "gemm_simt"} | ({"recurrent"} if self.weight_on == "input" else set())
+        libs = {"rowwise", "moe_route", "gemm_simt"} | ({"recurrent"} if self.weight_on == "input" or not self.gated else set())
         if self.runtime.fast_kernels and self.hidden >= 128:
             libs |= {"gemm_tc", "gemm_tc2"}
         return libs
@@ -178,7 +187,7 @@ class SparseMoE(Part):
                 out[e].copy_(self.fetch(source, self.expert_name(proj, e)))
             return out
 
-        self.w_gate = slab("gate", I, self.hidden)
+        self.w_gate = slab("gate", I, self.hidden) if self.gated else None
         self.w_up = slab("up", I, self.hidden)
         self.w_down = slab("down", self.hidden, I)
         if self.shared_inter > 0:
@@ -307,6 +316,13 @@ class SparseMoE(Part):
             project(rt, scaled, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, max_group_rows=T,
                     offsets_settled=True, act_limit=self.act_limit, act_alpha=self.act_alpha)
             wts = torch.ones_like(wts)
+        elif not self.gated:
+            # an expert without a gate: the product in float32, then the activation as it is rounded
+            pre = torch.empty((n_slots, self.inter), dtype=torch.float32, device=dev)
+            K.tag = "experts up"
+            project(rt, x, self.w_up[:G], pre, group_offsets=offsets, a_row_index=slot_token, max_group_rows=T)
+            K.tag = "experts activation"
+            K.relu2_rows(pre, act)
         else:
             K.tag = "experts gate/up"
             project(rt, x, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, a_row_index=slot_token,

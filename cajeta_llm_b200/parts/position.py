@@ -14,6 +14,10 @@ reference does (model/Prim.cajeta:1866-1880; per-layer state, model/Attention.ca
 the frequency is ``f_d / factor * ramp_d + f_d (1 - ramp_d)``, and the part offers ``magnitude`` =
 ``0.1 ln(factor) + 1``, by which a mixer multiplies cos and sin (1 without scaling).  The table is worked
 out in float64 and rounded once.
+``scaling`` with ``"kind": "wavelength"`` (keys ``factor``, ``low``, ``high``, ``original``) is the other common form: with
+the wavelength ``l = 2 pi / f``, a frequency stays where ``l < original / high``, becomes ``f / factor`` where
+``l > original / low``, and in between ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``;
+the magnitude stays 1.  Worked out in float64 and rounded once.
 ``none``: no rotation.
 """
 from __future__ import annotations
@@ -41,7 +45,17 @@ class RotaryEncoding(Part):
         inv = np.power(np.float32(self.theta), exponent).astype(np.float32)
         self.magnitude = 1.0
         scaling = spec.get("scaling")
-        if scaling:
+        if scaling and scaling.get("kind") == "wavelength":
+            factor, original = float(scaling["factor"]), float(scaling["original"])
+            low, high = float(scaling["low"]), float(scaling["high"])
+            if factor <= 0.0 or original <= 0.0 or not high > low >= 0.0:
+                raise ValueError("rope scaling by wavelength needs a positive factor and original length and high > low >= 0")
+            f = np.power(float(self.theta), -2.0 * np.arange(half, dtype=np.float64) / self.rotary_dim)
+            wavelength = 2.0 * math.pi / f
+            s = (original / wavelength - low) / (high - low)
+            mid = (1.0 - s) * f / factor + s * f
+            inv = np.where(wavelength < original / high, f, np.where(wavelength > original / low, f / factor, mid)).astype(np.float32)
+        elif scaling:
             factor, original = float(scaling["factor"]), float(scaling["original"])
             if factor <= 0.0 or original <= 0.0 or self.theta <= 1.0:
                 raise ValueError("rope scaling needs a positive factor and original length and theta > 1")
