@@ -1,7 +1,8 @@
-"""Throughput of a Balalorn or a Saropel model at layer sizes that resemble real models', beside the
-engine's Qwen2-MoE model at equal width, depth, experts and feed-forward sizes.
+"""Throughput of a Balalorn, a Saropel or a Govuvik model at layer sizes that resemble real models', beside the
+engine's Qwen2-MoE model at equal width, depth, experts and feed-forward sizes (Govuvik: beside Balalorn, the
+engine's other model with recurrent state, at equal width, depth and experts).
 
-``python bench.py --design balalorn|saropel [--sizes small,medium,large]`` prints one JSON line per
+``python bench.py --design balalorn|saropel|govuvik [--sizes small,medium,large]`` prints one JSON line per
 (size, model): prefill tokens a second (one prompt of 2,048 tokens), decode tokens a second
 (8 requests of 512 tokens each, steps replayed from CUDA graphs), and where the time of both
 steps goes by class of work (launches serialised, an event behind each), with the bytes or
@@ -60,6 +61,26 @@ def saropel_config(s):
                        {"type": "attention", "mixer": capped, "mlp": dense}]}
 
 
+GOVUVIK_WINDOW = 1024
+
+
+def govuvik_config(s):
+    """Four layers: matrix memory, two layers of windowed attention with mixed heads beside gated linear attention,
+    matrix memory; every layer with a routed feed-forward of ungated experts."""
+    h, H = s["width"], s["heads"]
+    memory = {"heads": H // 2, "dim": 128, "vdim": 256, "gate_cap": 15.0}
+    left = {"conv": 4, "dim": 128, "heads": H, "kv_heads": H // 4, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": GOVUVIK_WINDOW},
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"heads": H // 4, "dim": 128, "vdim": 256, "tau": 16.0, "decay_rank": 16}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
+    kinds = [lambda: {"type": "mlstm", "mixer": dict(memory), "mlp": moe},
+             lambda: {"type": "parallel", "mixer": {"left": dict(left), "right": dict(right)}, "mlp": moe},
+             lambda: {"type": "parallel", "mixer": {"left": dict(left), "right": dict(right)}, "mlp": moe},
+             lambda: {"type": "mlstm", "mixer": dict(memory), "mlp": moe}]
+    return {"architecture": "Govuvik", "width": h, "vocab": VOCAB, "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "logit_softcap": 30.0,
+            "layers": [kinds[i % 4]() for i in range(s["layers"])]}
+
+
 def qwen_config(s, shared=0):
     return {"architectures": ["Qwen2MoeForCausalLM"], "hidden_size": s["width"], "intermediate_size": s["ff"],
             "num_hidden_layers": s["layers"], "num_attention_heads": s["heads"], "num_key_value_heads": s["heads"], "head_dim": 128,
@@ -84,6 +105,18 @@ def needs(design, s, rows, ctx, prefill):
             else:
                 by += rows * min(ctx, w) * 2 * H * 128 * 2
         out["attention"] = (by, fl)
+        return out
+    if design == "govuvik":
+        n_mem, n_par = (L + 3) // 4 + L // 4, (L + 2) // 4 + (L + 1) // 4
+        w = GOVUVIK_WINDOW
+        out["attention"] = (rows * min(ctx, w) * 2 * (H // 4) * 128 * 2 * n_par if not prefill else 0,
+                            4 * H * 128 * sum(min(i + 1, w) for i in range(rows)) * n_par if prefill else 0)
+        reqs = 1 if prefill else rows
+        mem, gla = (H // 2) * (128 * 256 + 128 + 1) * 4, (H // 4) * 128 * 256 * 4
+        # a state is read and written once a request; every row brings q, k, v (and the decays) in float32
+        out["scan"] = (reqs * 2 * (n_mem * mem + n_par * gla)
+                       + rows * 4 * (n_mem * (H // 2) * (2 * 128 + 256 + 2) + n_par * (H // 4) * (3 * 128 + 256)),
+                       rows * (n_mem * (H // 2) * 128 * 256 * 6 + n_par * (H // 4) * 128 * 256 * 5))
         return out
     n_lat, n_ssd, n_delta = (L + 3) // 4 + L // 4, (L + 2) // 4, (L + 1) // 4
     width = s["rank"] + 64
@@ -112,8 +145,12 @@ def run(args, peaks) -> int:
     rng = np.random.default_rng(3)
     for size in [x for x in args.sizes.split(",") if x]:
         s = SIZES[size]
-        pair = ((("saropel", saropel_config(s)), ("qwen2_moe", qwen_config(s, shared=s["eff"]))) if args.design == "saropel"
-                else (("balalorn", balalorn_config(s)), ("qwen2_moe", qwen_config(s))))
+        if args.design == "saropel":
+            pair = (("saropel", saropel_config(s)), ("qwen2_moe", qwen_config(s, shared=s["eff"])))
+        elif args.design == "govuvik":
+            pair = (("govuvik", govuvik_config(s)), ("balalorn", balalorn_config(s)))
+        else:
+            pair = (("balalorn", balalorn_config(s)), ("qwen2_moe", qwen_config(s)))
         for design, cfg in pair:
             tokens = BATCH * (PROMPT + 128) + PREFILL + 64
             eng = LlmEngine.load(EngineOptions(config=cfg, random_weights=True, seed=11, dtype="bfloat16", ctx=PREFILL + 64, max_seqs=BATCH,

@@ -74,7 +74,7 @@ class GovuvikConfig(ModelConfig):
             raise ConfigError(f"{r.source}: required key 'norm.eps' is missing")
         eps = _number(r.source, "norm.eps", norm["eps"])
         canon = raw.get("canon")
-        taps = 1
+        taps = 0                      # no 'canon': the mixer reads the normed row as it is
         if canon is not None:
             _need_ints(r.source, "canon", canon, ("taps",))
             taps = canon["taps"]
@@ -102,7 +102,9 @@ class GovuvikConfig(ModelConfig):
 
     def to_json_dict(self) -> Dict[str, Any]:
         d: Dict[str, Any] = {"architecture": self.architecture, "width": self.width, "vocab": self.vocab,
-                             "norm": {"eps": self.norm_eps}, "canon": {"taps": self.canon_taps}, "layers": self.layers}
+                             "norm": {"eps": self.norm_eps}, "layers": self.layers}
+        if self.canon_taps:
+            d["canon"] = {"taps": self.canon_taps}
         if self.logit_softcap:
             d["logit_softcap"] = self.logit_softcap
         if self.eos_token_ids:

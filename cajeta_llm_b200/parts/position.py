@@ -54,7 +54,7 @@ class RotaryEncoding(Part):
             wavelength = 2.0 * math.pi / f
             s = (original / wavelength - low) / (high - low)
             mid = (1.0 - s) * f / factor + s * f
-            inv = np.where(wavelength < original / high, f, np.where(wavelength > original / low, f / factor, mid)).astype(np.float32)
+            inv = np.where(wavelength < original / high, f, np.where(wavelength > (original / low if low > 0.0 else np.inf), f / factor, mid)).astype(np.float32)
         elif scaling:
             factor, original = float(scaling["factor"]), float(scaling["original"])
             if factor <= 0.0 or original <= 0.0 or self.theta <= 1.0:

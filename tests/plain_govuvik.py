@@ -106,7 +106,8 @@ def windowed_attention(m: dict, W, pre: str, h: np.ndarray, eps: float) -> np.nd
     T = h.shape[0]
     H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q, k, v = h @ W[pre + "q"].T, h @ W[pre + "k"].T, h @ W[pre + "v"].T
-    q, k, v = causal_conv(q, W[pre + "q.conv"]), causal_conv(k, W[pre + "k.conv"]), causal_conv(v, W[pre + "v.conv"])
+    if m.get("conv"):
+        q, k, v = causal_conv(q, W[pre + "q.conv"]), causal_conv(k, W[pre + "k.conv"]), causal_conv(v, W[pre + "v.conv"])
     q = (rms(q, eps) * W[pre + "q.norm"]).reshape(T, H, dim)
     k = (rms(k, eps) * W[pre + "k.norm"]).reshape(T, G, dim)
     v = v.reshape(T, G, vdim)
@@ -115,8 +116,10 @@ def windowed_attention(m: dict, W, pre: str, h: np.ndarray, eps: float) -> np.nd
         f = rope_frequencies(rot)
         q = np.stack([rotate_half(q[t], t, f, rot["dims"]) for t in range(T)])
         k = np.stack([rotate_half(k[t], t, f, rot["dims"]) for t in range(T)])
-    window, scale = m["mask"]["size"], float(m["scale"])
+    window, scale = (m.get("mask") or {}).get("size") or T, float(m["scale"])
     temp, talk, sink = W[pre + "temp"], W[pre + "talk"], W[pre + "sink"]
+    if m.get("_no_sink"):
+        sink = np.full_like(sink, -np.inf)
     out = np.zeros((T, H, vdim))
     for t in range(T):
         lo = max(0, t - window + 1)
@@ -127,7 +130,7 @@ def windowed_attention(m: dict, W, pre: str, h: np.ndarray, eps: float) -> np.nd
         for hd in range(H):
             top = max(s[hd].max(), sink[hd])
             e = np.exp(s[hd] - top)
-            out[t, hd] = (e @ v[lo:t + 1, hd // (H // G)]) / (e.sum() + math.exp(sink[hd] - top))
+            out[t, hd] = (e @ v[lo:t + 1, hd // (H // G)]) / (e.sum() + np.exp(sink[hd] - top))
     return out.reshape(T, H * vdim) @ W[pre + "o"].T
 
 
@@ -185,7 +188,8 @@ def moe_ff(ff: dict, W, pre: str, h: np.ndarray, picked=None, gaps=None) -> np.n
 def layer(cfg, W, i: int, x: np.ndarray, picked=None, gaps=None) -> np.ndarray:
     spec, eps, pre = cfg["layers"][i], float(cfg["norm"]["eps"]), f"l{i}."
     h = rms(x, eps) * W[pre + "norm1"]
-    h = h + causal_conv(h, W[pre + "canon1"])
+    if cfg.get("canon"):
+        h = h + causal_conv(h, W[pre + "canon1"])
     if spec["type"] == "mlstm":
         y = mlstm_mixer(spec["mixer"], W, pre + "mix.", h, eps)
     elif spec["type"] == "parallel":
@@ -199,18 +203,22 @@ def layer(cfg, W, i: int, x: np.ndarray, picked=None, gaps=None) -> np.ndarray:
     return x
 
 
-def forward(cfg, W, tokens: List[int], keep_layers: bool = False, picks: Optional[list] = None, gaps: Optional[list] = None):
-    """Logits [T, vocab] of a whole sequence; with ``keep_layers`` also the stream after every layer."""
+def forward(cfg, W, tokens: List[int], keep_layers: bool = False, picks: Optional[dict] = None, gaps: Optional[dict] = None):
+    """Logits [T, vocab] of a whole sequence; with ``keep_layers`` also the stream after every layer.  ``picks`` /
+    ``gaps`` (dicts) receive, by a routed feed-forward's tensor-name prefix, every token's experts and the gap
+    between the last picked logit and the next."""
     eps = float(cfg["norm"]["eps"])
     x = rms(W["embed"][np.asarray(tokens)].astype(np.float64), eps) * W["embed.norm"]
     kept = []
     for i in range(len(cfg["layers"])):
-        x = layer(cfg, W, i, x, picks, gaps)
+        routed = cfg["layers"][i].get("mlp") is not None
+        x = layer(cfg, W, i, x, picks.setdefault(f"l{i}.mlp", []) if picks is not None and routed else None,
+                  gaps.setdefault(f"l{i}.mlp", []) if gaps is not None and routed else None)
         if keep_layers:
             kept.append(x.copy())
     z = (rms(x, eps) * W["final.norm"]) @ W["head"].T
-    cap = float(cfg["logit_softcap"])
-    logits = cap * np.tanh(z / cap)
+    cap = float(cfg.get("logit_softcap") or 0.0)
+    logits = cap * np.tanh(z / cap) if cap else z
     return (logits, np.stack(kept)) if keep_layers else logits
 
 
