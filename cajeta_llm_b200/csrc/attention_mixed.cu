@@ -1,0 +1,379 @@
+// Attention whose heads' scores are mixed before the softmax, with a sink, for bfloat16 storage: a tile of
+// 16 query rows of one request and ALL heads, worked on by a thread-block cluster.
+//
+//   raw_g,ij = q_g,i . k_j                                         tensor cores (mma.sync, bf16 x bf16 -> f32)
+//   s_h,ij   = sum_g talk[h, g] temp[g] scale raw_g,ij             float32, FMA units
+//   o_h,i    = sum_j e^(s_h,ij - m) v_j / (sum_j e^(s_h,ij - m) + e^(sink_h - m))
+// over the keys j of row i's window [p_i + 1 - w, p_i].  The mixing needs every head's raw score of a
+// (row, key) pair, while the output accumulators of all heads (heads x 16 x vd float32) do not fit one SM.
+// So the heads are dealt to the C blocks of a cluster, H / C <= 8 heads each, one head a warp: a block
+// computes the raw scores of ITS heads for a chunk of 32 keys into its shared memory, the cluster meets,
+// every block reads all blocks' raw scores through distributed shared memory and mixes them for its own
+// output heads (a thread owns two adjacent keys of a row and all of the block's heads, so a raw score is
+// read once per block and used for up to 8 products), and then each warp runs the running softmax and
+// the weighted sum of values for its head.  A block loads only the key and value heads its own heads use.
+// The softmax's weights stay float32 in effect: a weight enters the value product as two bfloat16 terms
+// (its rounding and the rest), both accumulated in float32.  The sum over g runs in the order of g
+// whatever C is, so the result does not depend on the cluster's size.  The cluster barrier is the
+// hardware's (barrier.cluster): no block spins on memory.
+//
+// The sink has no key and no value, is neither scaled nor multiplied by temp, and counts once: the
+// running maximum starts at sink_h and the running sum at 1.
+#include "common.cuh"
+
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+using namespace cj;
+
+namespace {
+
+constexpr int BM = 16;                // query rows a tile
+constexpr int BN = 32;                // keys a chunk
+constexpr int WARPS = 8;              // = the most heads a block owns
+constexpr int THREADS = WARPS * 32;
+constexpr int KT_MAX = 8;             // 16-wide steps over a head's size: hd <= 128
+constexpr int VT_MAX = 16;            // 8-wide tiles over a value's size: vd <= 128
+constexpr int RS = BN + 8;            // row stride of a score tile, floats
+constexpr int VS = BN + 8;            // key stride of the transposed values, bf16
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// a pair of float32 as (rounded to bf16, the rest rounded to bf16), each pair packed in a word
+__device__ __forceinline__ void split_pair(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const bf16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+    const bf16 xl = __float2bfloat16_rn(x - __bfloat162float(xh)), yl = __float2bfloat16_rn(y - __bfloat162float(yh));
+    hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
+    lo = (uint32_t)__bfloat16_as_ushort(xl) | ((uint32_t)__bfloat16_as_ushort(yl) << 16);
+}
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// the key/value heads that the heads [g_lo, g_lo + hl) use
+__host__ __device__ inline void kv_range(int g_lo, int hl, int per_kv, int& kv_lo, int& n) {
+    kv_lo = g_lo / per_kv;
+    n = (g_lo + hl - 1) / per_kv - kv_lo + 1;
+}
+
+__global__ void __launch_bounds__(THREADS) mixed_heads_tile_kernel(
+    const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ kplane, const bf16* __restrict__ vplane,
+    const int* __restrict__ positions, const int* __restrict__ req_start, int n_requests, const int* __restrict__ table,
+    int table_stride, int page_tokens, int n_heads, int n_kv, int hd, int vd, int window, float scale,
+    const float* __restrict__ temp, const float* __restrict__ talk, const float* __restrict__ sink, int kv_local_max) {
+    cj::after_predecessor();
+    cj::release_successor();
+    cg::cluster_group cluster = cg::this_cluster();
+    const int C = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int HL = n_heads / C, g_lo = crank * HL, per_kv = n_heads / n_kv;
+    int kv_lo, nkvl;
+    kv_range(g_lo, HL, per_kv, kv_lo, nkvl);
+    const int hdp = (hd + 15) & ~15, KT = hdp / 16, VT = vd / 8, KS = hdp + 8;
+
+    // ---- which request and which 16-row tile of it: the same for every block of the cluster ----
+    int tile = (int)(gridDim.x / C) - 1 - (int)(blockIdx.x / C), req = -1, row0 = 0, rows = 0, first = 0;
+    for (int r = 0; r < n_requests; ++r) {
+        const int lo = req_start[r], hi = req_start[r + 1];
+        const int tiles = (hi - lo + BM - 1) / BM;
+        if (tile < first + tiles) {
+            req = r;
+            row0 = lo + (tile - first) * BM;
+            rows = min(BM, hi - row0);
+            break;
+        }
+        first += tiles;
+    }
+    if (req < 0) return;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* raw = (float*)smem_raw;                         // [HL][BM][RS] raw scores of this block's heads
+    float* mixed = raw + HL * BM * RS;                     // [HL][BM][RS] mixed scores of this block's heads
+    float* ct = mixed + HL * BM * RS;                      // [n_heads][8]: what raw head g gives to local head u
+    bf16* ks = (bf16*)(ct + n_heads * 8);                  // [kv_local_max][BN][KS]
+    bf16* vt = ks + (size_t)kv_local_max * BN * KS;        // [kv_local_max][vd][VS], keys contiguous
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
+    const int p0 = positions[row0], p_last = p0 + rows - 1;
+    const int key_from = (window > 0 && p0 + 1 > window) ? p0 + 1 - window : 0;
+    const int n_chunks = (p_last - key_from) / BN + 1;
+    const int* tab = table + (size_t)req * table_stride;
+
+    for (int i = tid; i < n_heads * 8; i += THREADS) {
+        const int g = i >> 3, u = i & 7;
+        float c = 0.0f;
+        if (u < HL) {
+            c = talk ? talk[(size_t)(g_lo + u) * n_heads + g] : (g == g_lo + u ? 1.0f : 0.0f);
+            c *= scale * (temp ? temp[g] : 1.0f);
+        }
+        ct[i] = c;
+    }
+    {   // the stretch of a key row past hd is multiplied by zeros of q: it must not hold a NaN
+        uint32_t* z = (uint32_t*)ks;
+        const int words = kv_local_max * BN * KS / 2;
+        for (int i = tid; i < words; i += THREADS) z[i] = 0u;
+    }
+
+    // ---- this warp's head: query fragments, running maximum and sum, output accumulators ----
+    const bool has_head = warp < HL;
+    const int head = g_lo + warp;
+    uint32_t qa[KT_MAX][4];
+    float o[VT_MAX][4];
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+#pragma unroll
+    for (int kt = 0; kt < KT_MAX; ++kt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) qa[kt][e] = 0u;
+        if (has_head && kt < KT) {
+            const int c = kt * 16 + cq;
+            const bf16* q0 = q + ((size_t)(row0 + r0) * n_heads + head) * hd;
+            const bf16* q1 = q + ((size_t)(row0 + r1) * n_heads + head) * hd;
+            if (r0 < rows && c < hd) qa[kt][0] = *(const uint32_t*)(q0 + c);
+            if (r1 < rows && c < hd) qa[kt][1] = *(const uint32_t*)(q1 + c);
+            if (r0 < rows && c + 8 < hd) qa[kt][2] = *(const uint32_t*)(q0 + c + 8);
+            if (r1 < rows && c + 8 < hd) qa[kt][3] = *(const uint32_t*)(q1 + c + 8);
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < VT_MAX; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.0f;
+    if (has_head && sink) {
+        m0 = m1 = sink[head];
+        l0 = l1 = 1.0f;
+    }
+    const int kvl = has_head ? head / per_kv - kv_lo : 0;
+    __syncthreads();
+
+    for (int c = 0; c < n_chunks; ++c) {
+        const int key0 = key_from + c * BN;
+        // ---- keys as they lie, values transposed (two neighbouring keys of a column in one word) ----
+        {
+            const int ch_k = hd / 8;
+            for (int i = tid; i < nkvl * BN * ch_k; i += THREADS) {
+                const int ch = i % ch_k, r = (i / ch_k) % BN, kv = i / (ch_k * BN);
+                const int key = key0 + r;
+                uint4 val = make_uint4(0u, 0u, 0u, 0u);
+                if (key <= p_last) {
+                    const int page = tab[key / page_tokens];
+                    if (page >= 0)
+                        val = *(const uint4*)(kplane + (((size_t)page * n_kv + kv_lo + kv) * page_tokens + key % page_tokens) * hd + ch * 8);
+                }
+                *(uint4*)(ks + ((size_t)kv * BN + r) * KS + ch * 8) = val;
+            }
+            for (int i = tid; i < nkvl * BN * VT; i += THREADS) {
+                const int r = i % BN, ch = (i / BN) % VT, kv = i / (BN * VT);
+                const int key = key0 + r;
+                uint4 val = make_uint4(0u, 0u, 0u, 0u);
+                if (key <= p_last) {
+                    const int page = tab[key / page_tokens];
+                    if (page >= 0)
+                        val = *(const uint4*)(vplane + (((size_t)page * n_kv + kv_lo + kv) * page_tokens + key % page_tokens) * vd + ch * 8);
+                }
+                const unsigned short* e = (const unsigned short*)&val;
+                unsigned short* dst = (unsigned short*)(vt + ((size_t)kv * vd + ch * 8) * VS + r);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) dst[k * VS] = e[k];
+            }
+        }
+        __syncthreads();
+        if (c > 0) cluster_wait();                         // every block has read the last chunk's raw scores
+
+        // ---- raw scores of this warp's head ----
+        if (has_head) {
+#pragma unroll
+            for (int nt = 0; nt < BN / 8; ++nt) {
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const bf16* krow = ks + ((size_t)kvl * BN + nt * 8 + r0) * KS + cq;
+#pragma unroll
+                for (int kt = 0; kt < KT_MAX; ++kt)
+                    if (kt < KT) mma_bf16(acc, qa[kt], *(const uint32_t*)(krow + kt * 16), *(const uint32_t*)(krow + kt * 16 + 8));
+                *(float2*)(raw + ((size_t)warp * BM + r0) * RS + nt * 8 + cq) = make_float2(acc[0], acc[1]);
+                *(float2*)(raw + ((size_t)warp * BM + r1) * RS + nt * 8 + cq) = make_float2(acc[2], acc[3]);
+            }
+        }
+        cluster_arrive();
+        cluster_wait();                                    // all heads' raw scores of the chunk are written
+
+        // ---- mixing: a thread owns two adjacent keys of a row, and the block's heads ----
+        {
+            const int i = tid >> 4, j = (tid & 15) * 2;
+            float a[8][2];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a[u][0] = a[u][1] = 0.0f;
+            for (int rr = 0; rr < C; ++rr) {
+                const float* theirs = cluster.map_shared_rank(raw, rr);
+                for (int gl = 0; gl < HL; ++gl) {
+                    const float2 x = *(const float2*)(theirs + ((size_t)gl * BM + i) * RS + j);
+                    const float4 c0 = *(const float4*)(ct + (size_t)(rr * HL + gl) * 8);
+                    const float4 c1 = *(const float4*)(ct + (size_t)(rr * HL + gl) * 8 + 4);
+                    a[0][0] = fmaf(c0.x, x.x, a[0][0]); a[0][1] = fmaf(c0.x, x.y, a[0][1]);
+                    a[1][0] = fmaf(c0.y, x.x, a[1][0]); a[1][1] = fmaf(c0.y, x.y, a[1][1]);
+                    a[2][0] = fmaf(c0.z, x.x, a[2][0]); a[2][1] = fmaf(c0.z, x.y, a[2][1]);
+                    a[3][0] = fmaf(c0.w, x.x, a[3][0]); a[3][1] = fmaf(c0.w, x.y, a[3][1]);
+                    a[4][0] = fmaf(c1.x, x.x, a[4][0]); a[4][1] = fmaf(c1.x, x.y, a[4][1]);
+                    a[5][0] = fmaf(c1.y, x.x, a[5][0]); a[5][1] = fmaf(c1.y, x.y, a[5][1]);
+                    a[6][0] = fmaf(c1.z, x.x, a[6][0]); a[6][1] = fmaf(c1.z, x.y, a[6][1]);
+                    a[7][0] = fmaf(c1.w, x.x, a[7][0]); a[7][1] = fmaf(c1.w, x.y, a[7][1]);
+                }
+            }
+            cluster_arrive();                              // done with the other blocks' raw scores
+            const int p_i = p0 + min(i, rows - 1);
+            const int ka = key0 + j, kb = ka + 1;
+            const bool va = ka <= p_i && (window <= 0 || ka > p_i - window);
+            const bool vb = kb <= p_i && (window <= 0 || kb > p_i - window);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (u < HL)
+                    *(float2*)(mixed + ((size_t)u * BM + i) * RS + j) = make_float2(va ? a[u][0] : -INFINITY, vb ? a[u][1] : -INFINITY);
+        }
+        __syncthreads();
+
+        // ---- running softmax and the weighted sum of values of this warp's head ----
+        if (has_head) {
+            float2 s0[BN / 8], s1[BN / 8];
+            float x0 = -INFINITY, x1 = -INFINITY;
+#pragma unroll
+            for (int t = 0; t < BN / 8; ++t) {
+                s0[t] = *(const float2*)(mixed + ((size_t)warp * BM + r0) * RS + t * 8 + cq);
+                s1[t] = *(const float2*)(mixed + ((size_t)warp * BM + r1) * RS + t * 8 + cq);
+                x0 = fmaxf(x0, fmaxf(s0[t].x, s0[t].y));
+                x1 = fmaxf(x1, fmaxf(s1[t].x, s1[t].y));
+            }
+            const float n0 = fmaxf(m0, quad_max(x0)), n1 = fmaxf(m1, quad_max(x1));
+            const float u0 = n0 == -INFINITY ? 0.0f : n0, u1 = n1 == -INFINITY ? 0.0f : n1;   // nothing seen yet: all terms 0
+            const float f0 = expf(m0 - u0), f1 = expf(m1 - u1);
+            float e0 = 0.0f, e1 = 0.0f;
+#pragma unroll
+            for (int t = 0; t < BN / 8; ++t) {
+                s0[t].x = expf(s0[t].x - u0); s0[t].y = expf(s0[t].y - u0);
+                s1[t].x = expf(s1[t].x - u1); s1[t].y = expf(s1[t].y - u1);
+                e0 += s0[t].x + s0[t].y;
+                e1 += s1[t].x + s1[t].y;
+            }
+            l0 = l0 * f0 + quad_sum(e0);
+            l1 = l1 * f1 + quad_sum(e1);
+            m0 = n0;
+            m1 = n1;
+#pragma unroll
+            for (int v = 0; v < VT_MAX; ++v) { o[v][0] *= f0; o[v][1] *= f0; o[v][2] *= f1; o[v][3] *= f1; }
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) {
+                uint32_t hi[4], lo[4];
+                split_pair(s0[2 * kk].x, s0[2 * kk].y, hi[0], lo[0]);
+                split_pair(s1[2 * kk].x, s1[2 * kk].y, hi[1], lo[1]);
+                split_pair(s0[2 * kk + 1].x, s0[2 * kk + 1].y, hi[2], lo[2]);
+                split_pair(s1[2 * kk + 1].x, s1[2 * kk + 1].y, hi[3], lo[3]);
+                const bf16* vcol = vt + ((size_t)kvl * vd + r0) * VS + kk * 16 + cq;
+#pragma unroll
+                for (int v = 0; v < VT_MAX; ++v) {
+                    if (v < VT) {
+                        const uint32_t b0 = *(const uint32_t*)(vcol + (size_t)v * 8 * VS), b1 = *(const uint32_t*)(vcol + (size_t)v * 8 * VS + 8);
+                        mma_bf16(o[v], hi, b0, b1);
+                        mma_bf16(o[v], lo, b0, b1);
+                    }
+                }
+            }
+        }
+        __syncthreads();                                   // the chunk's keys, values and mixed scores are free again
+    }
+    cluster_wait();                                        // no block leaves while another may still read its raw scores
+
+    if (has_head) {
+        const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+        bf16* o0 = out + ((size_t)(row0 + r0) * n_heads + head) * vd + cq;
+        bf16* o1 = out + ((size_t)(row0 + r1) * n_heads + head) * vd + cq;
+#pragma unroll
+        for (int v = 0; v < VT_MAX; ++v) {
+            if (v < VT) {
+                if (r0 < rows) *(__nv_bfloat162*)(o0 + v * 8) = __floats2bfloat162_rn(o[v][0] * i0, o[v][1] * i0);
+                if (r1 < rows) *(__nv_bfloat162*)(o1 + v * 8) = __floats2bfloat162_rn(o[v][2] * i1, o[v][3] * i1);
+            }
+        }
+    }
+}
+
+// the cluster's size for these heads: the smallest of 1, 2, 4, 8 that leaves a block at most 8 heads; 0: none
+inline int cluster_for(int n_heads) {
+    for (int c = 1; c <= 8; c *= 2)
+        if (n_heads % c == 0 && n_heads / c <= WARPS) return c;
+    return 0;
+}
+
+inline size_t tile_smem(int n_heads, int n_kv, int hd, int vd, int C, int& kv_local_max) {
+    const int HL = n_heads / C, per_kv = n_heads / n_kv, hdp = (hd + 15) & ~15;
+    kv_local_max = 1;
+    for (int r = 0; r < C; ++r) {
+        int lo, n;
+        kv_range(r * HL, HL, per_kv, lo, n);
+        if (n > kv_local_max) kv_local_max = n;
+    }
+    return (size_t)2 * HL * BM * RS * sizeof(float) + (size_t)n_heads * 8 * sizeof(float) +
+           (size_t)kv_local_max * BN * (hdp + 8) * sizeof(bf16) + (size_t)kv_local_max * vd * VS * sizeof(bf16);
+}
+
+}  // namespace
+
+// 1 if the tiled form takes these sizes (bfloat16 storage, head and value sizes multiples of 8 up to 128,
+// heads that a cluster of at most 8 blocks can deal out 8 a block), else 0: the caller then uses the
+// row-at-a-time form.
+CJ_EXPORT int cj_mixed_heads_tile_fits(int n_heads, int n_kv, int hd, int vd) {
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return 0;
+    if (hd <= 0 || vd <= 0 || hd % 8 != 0 || vd % 8 != 0 || hd > 16 * KT_MAX || vd > 8 * VT_MAX) return 0;
+    const int C = cluster_for(n_heads);
+    if (C == 0) return 0;
+    int kvm;
+    return tile_smem(n_heads, n_kv, hd, vd, C, kvm) <= 200 * 1024 ? 1 : 0;
+}
+
+// q [T, n_heads, hd], out [T, n_heads, vd], planes [pages, n_kv, page_tokens, hd | vd]: bfloat16.  req_start
+// [n_requests + 1]: the rows of request r are [req_start[r], req_start[r + 1]), at consecutive positions.
+// temp [n_heads], talk [n_heads, n_heads], sink [n_heads]: float32 or null.
+CJ_EXPORT int cj_mixed_heads_attention_tile(const void* q, void* out, const void* kplane, const void* vplane, const int* positions,
+                                            const int* req_start, int n_requests, int total_rows, const int* table, int table_stride,
+                                            int page_tokens, int n_heads, int n_kv, int hd, int vd, int window, float scale,
+                                            const float* temp, const float* talk, const float* sink, cudaStream_t stream) {
+    if (total_rows <= 0 || n_requests <= 0) return 0;
+    if (!q || !out || !kplane || !vplane || !positions || !req_start || !table) return CJ_ERR_ARG;
+    if (!cj_mixed_heads_tile_fits(n_heads, n_kv, hd, vd) || page_tokens <= 0) return CJ_ERR_SIZE;
+    const int tiles = (total_rows + BM - 1) / BM + n_requests;
+    int C = cluster_for(n_heads);
+    // few tiles (single decoded tokens): smaller shares of the heads on more SMs
+    while (C < 8 && n_heads % (2 * C) == 0 && tiles * C < 128) C *= 2;
+    int kvm;
+    const size_t smem = tile_smem(n_heads, n_kv, hd, vd, C, kvm);
+    static size_t sized = 48 * 1024;
+    if (smem > sized) {
+        cudaError_t e = cudaFuncSetAttribute(mixed_heads_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        sized = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * C);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = C;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, mixed_heads_tile_kernel, (const bf16*)q, (bf16*)out, (const bf16*)kplane, (const bf16*)vplane, positions,
+                       req_start, n_requests, table, table_stride, page_tokens, n_heads, n_kv, hd, vd, window, scale, temp, talk,
+                       sink, kvm);
+    return launch_status();
+}

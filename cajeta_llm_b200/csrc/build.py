@@ -34,6 +34,7 @@ LIBRARIES: Dict[str, str] = {
     "rowwise": "rowwise.cu",
     "gemm_simt": "gemm_simt.cu",
     "attention_paged": "attention_paged.cu",
+    "attention_mixed": "attention_mixed.cu",
     "moe_route": "moe_route.cu",
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",

@@ -279,14 +279,35 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v
     _check(st, "paged_attention")
 
 
+def mixed_heads_tile_shape(n_heads: int, n_kv: int, head_dim: int, value_dim: int) -> bool:
+    """Whether the tiled form of the mixed-heads attention takes these sizes: head and value sizes multiples of 8 up
+    to 128, and heads that 1, 2, 4 or 8 blocks share out evenly, at most 8 a block.  A matter of arithmetic: the
+    library is not asked."""
+    if n_heads <= 0 or n_kv <= 0 or n_heads % n_kv or head_dim <= 0 or value_dim <= 0:
+        return False
+    if head_dim % 8 or value_dim % 8 or head_dim > 128 or value_dim > 128:
+        return False
+    for c in (1, 2, 4, 8):
+        if n_heads % c == 0 and n_heads // c <= 8:
+            hl, per = n_heads // c, n_heads // n_kv
+            kv = max((r * hl + hl - 1) // per - (r * hl) // per + 1 for r in range(c))
+            hdp = (head_dim + 15) // 16 * 16
+            return 2 * hl * 16 * 40 * 4 + n_heads * 32 + kv * 32 * (hdp + 8) * 2 + kv * value_dim * 40 * 2 <= 200 * 1024
+    return False
+
+
 def mixed_heads_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                           positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
                           n_heads: int, n_kv: int, head_dim: int, value_dim: int, window: int, scale: float,
                           temp: Optional[torch.Tensor] = None, talk: Optional[torch.Tensor] = None,
-                          sink: Optional[torch.Tensor] = None) -> None:
+                          sink: Optional[torch.Tensor] = None, req_start: Optional[torch.Tensor] = None,
+                          n_requests: int = 0) -> None:
     """Attention of every row over its request's cached keys [from, position] in which the heads' scores are mixed
     before the softmax: raw_g = (q_g . k) scale temp[g]; s_h = sum_g talk[h, g] raw_g; the softmax's divisor also
-    holds exp(sink[h]).  ``temp`` [heads], ``talk`` [heads, heads], ``sink`` [heads]: float32, each optional."""
+    holds exp(sink[h]).  ``temp`` [heads], ``talk`` [heads, heads], ``sink`` [heads]: float32, each optional.
+    With ``req_start`` (int32 ``[n_requests + 1]``, the first row of each request; a request's rows at consecutive
+    positions) and sizes that ``mixed_heads_tile_shape`` takes, bfloat16 rows run in the tiled form: 16 rows of a
+    request and all heads on a cluster of blocks, the products on tensor cores."""
     _need(q, "q"), _need(out, "out"), _need(k_plane, "k_plane"), _need(v_plane, "v_plane")
     _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
     for n, t, size in (("temp", temp, n_heads), ("talk", talk, n_heads * n_heads), ("sink", sink, n_heads)):
@@ -294,6 +315,15 @@ def mixed_heads_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Ten
             _need(t, n, torch.float32)
             if t.numel() != size:
                 raise KernelError(f"mixed_heads_attention: {n} must hold {size} entries, found {t.numel()}")
+    if (req_start is not None and n_requests > 0 and q.dtype == torch.bfloat16 and k_plane.dtype == torch.bfloat16
+            and mixed_heads_tile_shape(n_heads, n_kv, head_dim, value_dim or head_dim)):
+        _need(req_start, "req_start", torch.int32)
+        st = library("attention_mixed").cj_mixed_heads_attention_tile(
+            _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(positions), _ptr(req_start), _i(n_requests), _i(q.shape[0]),
+            _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_heads), _i(n_kv), _i(head_dim), _i(value_dim or head_dim),
+            _i(window), _f(scale), _ptr(temp), _ptr(talk), _ptr(sink), _stream())
+        _check(st, "mixed_heads_attention (tiled)")
+        return
     st = library("attention_paged").cj_mixed_heads_attention(
         _ptr(q), _ptr(out), _i(_code(q)), _ptr(k_plane), _ptr(v_plane), _i(_code(k_plane)), _ptr(positions),
         _ptr(row_req), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(q.shape[0]), _i(n_heads), _i(n_kv), _i(head_dim),

@@ -159,6 +159,8 @@ class PagedAttention(Part):
         libs = {"rowwise", "gemm_simt"}
         if self.mixed:
             libs |= {"attention_paged"} | ({"recurrent"} if self.proj_conv else set())
+            if self._tiled():
+                libs.add("attention_mixed")
         elif self.general:
             libs.add("attention_paged")
             if self.runtime.fast_kernels and self.value_dim == self.head_dim:
@@ -293,6 +295,13 @@ class PagedAttention(Part):
         K.tag = None
         return parts
 
+    def _tiled(self) -> bool:
+        """Whether the mixed-heads attention runs in its tiled form (tensor cores, a cluster over the heads): bfloat16
+        storage and sizes the form takes; float32 runs, and other sizes, take the row-at-a-time form."""
+        rt = self.runtime
+        return bool(rt.fast_kernels and rt.act_dtype == torch.bfloat16 and rt.cache_dtype == torch.bfloat16
+                    and K.mixed_heads_tile_shape(self.heads, self.kv_heads, self.head_dim, self.value_dim))
+
     def _forward_mixed(self, x: torch.Tensor, residual: torch.Tensor, ctx, entry) -> None:
         """The path of a mixer whose projections are convolved over time, whose norm spans all heads, or whose heads'
         scores are scaled, mixed or joined by a sink: one product for q | k | v, the convolution with its state, heads made
@@ -325,7 +334,8 @@ class PagedAttention(Part):
         K.tag = "attention"
         K.mixed_heads_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
                                 entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.value_dim, self.window,
-                                self.scale, temp=self.temp_w, talk=self.talk_w, sink=self.sink_w)
+                                self.scale, temp=self.temp_w, talk=self.talk_w, sink=self.sink_w,
+                                req_start=ctx.req_start if self._tiled() else None, n_requests=ctx.n_requests)
         K.tag = "o"
         project(rt, out.view(T, self.o_dim), self.w_o, residual, accumulate=True)
         K.tag = None

