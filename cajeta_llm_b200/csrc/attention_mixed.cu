@@ -35,7 +35,7 @@ constexpr int THREADS = WARPS * 32;
 constexpr int KT_MAX = 8;             // 16-wide steps over a head's size: hd <= 128
 constexpr int VT_MAX = 16;            // 8-wide tiles over a value's size: vd <= 128
 constexpr int RS = BN + 8;            // row stride of a score tile, floats
-constexpr int VS = BN + 8;            // key stride of the transposed values, bf16
+constexpr float LOG2E = 1.4426950408889634f;
 
 typedef __nv_bfloat16 bf16;
 
@@ -46,14 +46,15 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // a pair of float32 as (rounded to bf16, the rest rounded to bf16), each pair packed in a word
 __device__ __forceinline__ void split_pair(float x, float y, uint32_t& hi, uint32_t& lo) {
-    const bf16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
-    const bf16 xl = __float2bfloat16_rn(x - __bfloat162float(xh)), yl = __float2bfloat16_rn(y - __bfloat162float(yh));
-    hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
-    lo = (uint32_t)__bfloat16_as_ushort(xl) | ((uint32_t)__bfloat16_as_ushort(yl) << 16);
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);              // one conversion for the pair
+    hi = *(const uint32_t*)&h;
+    const __nv_bfloat162 l = __floats2bfloat162_rn(x - __uint_as_float(hi << 16), y - __uint_as_float(hi & 0xffff0000u));
+    lo = *(const uint32_t*)&l;
 }
 __device__ __forceinline__ float quad_max(float v) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
@@ -70,7 +71,25 @@ __host__ __device__ inline void kv_range(int g_lo, int hl, int per_kv, int& kv_l
     n = (g_lo + hl - 1) / per_kv - kv_lo + 1;
 }
 
-__global__ void __launch_bounds__(THREADS) mixed_heads_tile_kernel(
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// 16 bytes global -> shared without a register in between; not valid: the 16 bytes become zeros
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// four 8x8 bf16 matrices, lane l gives the address of row l % 8 of matrix l / 8
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+
+__global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
     const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ kplane, const bf16* __restrict__ vplane,
     const int* __restrict__ positions, const int* __restrict__ req_start, int n_requests, const int* __restrict__ table,
     int table_stride, int page_tokens, int n_heads, int n_kv, int hd, int vd, int window, float scale,
@@ -82,7 +101,7 @@ __global__ void __launch_bounds__(THREADS) mixed_heads_tile_kernel(
     const int HL = n_heads / C, g_lo = crank * HL, per_kv = n_heads / n_kv;
     int kv_lo, nkvl;
     kv_range(g_lo, HL, per_kv, kv_lo, nkvl);
-    const int hdp = (hd + 15) & ~15, KT = hdp / 16, VT = vd / 8, KS = hdp + 8;
+    const int hdp = (hd + 15) & ~15, KT = hdp / 16, VT = vd / 8, KS = hdp + 8, VR = vd + 8;
 
     // ---- which request and which 16-row tile of it: the same for every block of the cluster ----
     int tile = (int)(gridDim.x / C) - 1 - (int)(blockIdx.x / C), req = -1, row0 = 0, rows = 0, first = 0;
@@ -103,8 +122,9 @@ __global__ void __launch_bounds__(THREADS) mixed_heads_tile_kernel(
     float* raw = (float*)smem_raw;                         // [HL][BM][RS] raw scores of this block's heads
     float* mixed = raw + HL * BM * RS;                     // [HL][BM][RS] mixed scores of this block's heads
     float* ct = mixed + HL * BM * RS;                      // [n_heads][8]: what raw head g gives to local head u
-    bf16* ks = (bf16*)(ct + n_heads * 8);                  // [kv_local_max][BN][KS]
-    bf16* vt = ks + (size_t)kv_local_max * BN * KS;        // [kv_local_max][vd][VS], keys contiguous
+    bf16* qs = (bf16*)(ct + n_heads * 8);                  // [HL][BM][KS]
+    bf16* ks = qs + (size_t)HL * BM * KS;                  // [kv_local_max][BN][KS]
+    bf16* vs = ks + (size_t)kv_local_max * BN * KS;        // [kv_local_max][BN][VR]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
@@ -118,94 +138,116 @@ __global__ void __launch_bounds__(THREADS) mixed_heads_tile_kernel(
         float c = 0.0f;
         if (u < HL) {
             c = talk ? talk[(size_t)(g_lo + u) * n_heads + g] : (g == g_lo + u ? 1.0f : 0.0f);
-            c *= scale * (temp ? temp[g] : 1.0f);
+            c *= scale * (temp ? temp[g] : 1.0f) * LOG2E;      // mixed scores come out in units of log 2: e^s = 2^(s log2 e)
         }
         ct[i] = c;
     }
-    {   // the stretch of a key row past hd is multiplied by zeros of q: it must not hold a NaN
-        uint32_t* z = (uint32_t*)ks;
-        const int words = kv_local_max * BN * KS / 2;
+    {   // the stretch of a query or key row past hd enters the products: zeros, not whatever lay there
+        uint32_t* z = (uint32_t*)qs;
+        const int words = (HL * BM + kv_local_max * BN) * KS / 2;
         for (int i = tid; i < words; i += THREADS) z[i] = 0u;
     }
+    __syncthreads();
 
-    // ---- this warp's head: query fragments, running maximum and sum, output accumulators ----
+    const int ch_k = hd / 8;
+    __shared__ long long place[2][BN];                     // a chunk's keys in the planes, in (token, kv head 0) entries; -1: none
+    auto find_places = [&](int c) {                        // by the first warp; read after the block's next meeting
+        if (tid < BN) {
+            const int key = key_from + c * BN + tid;
+            long long at = -1;
+            if (c < n_chunks && key <= p_last) {
+                const int page = tab[key / page_tokens];
+                if (page >= 0) at = (long long)page * n_kv * page_tokens + key % page_tokens;
+            }
+            place[c & 1][tid] = at;
+        }
+    };
+    auto load_keys = [&](int c) {
+        const long long* at = place[c & 1];
+        for (int kv = 0; kv < nkvl; ++kv)
+            for (int i = tid; i < BN * ch_k; i += THREADS) {
+                const int r = i / ch_k, ch = i - r * ch_k;
+                const bool valid = at[r] >= 0;
+                cp_async16(ks + ((size_t)kv * BN + r) * KS + ch * 8,
+                           kplane + (valid ? ((size_t)at[r] + (size_t)(kv_lo + kv) * page_tokens) * hd + ch * 8 : 0), valid);
+            }
+    };
+    auto load_values = [&](int c) {
+        const long long* at = place[c & 1];
+        for (int kv = 0; kv < nkvl; ++kv)
+            for (int i = tid; i < BN * VT; i += THREADS) {
+                const int r = i / VT, ch = i - r * VT;
+                const bool valid = at[r] >= 0;
+                cp_async16(vs + ((size_t)kv * BN + r) * VR + ch * 8,
+                           vplane + (valid ? ((size_t)at[r] + (size_t)(kv_lo + kv) * page_tokens) * vd + ch * 8 : 0), valid);
+            }
+    };
+    find_places(0);
+    __syncthreads();
+    // the tile's queries of this block's heads, then the first chunk's keys, then its values: three groups
+    for (int i = tid; i < HL * BM * ch_k; i += THREADS) {
+        const int ch = i % ch_k, r = (i / ch_k) % BM, u = i / (ch_k * BM);
+        const bool valid = r < rows;
+        cp_async16(qs + ((size_t)u * BM + r) * KS + ch * 8, q + ((size_t)(row0 + (valid ? r : 0)) * n_heads + g_lo + u) * hd + ch * 8, valid);
+    }
+    cp_async_commit();
+    load_keys(0);
+    cp_async_commit();
+    load_values(0);
+    cp_async_commit();
+
+    // ---- this warp's head: running maximum and sum, output accumulators ----
     const bool has_head = warp < HL;
     const int head = g_lo + warp;
-    uint32_t qa[KT_MAX][4];
     float o[VT_MAX][4];
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
-    for (int kt = 0; kt < KT_MAX; ++kt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) qa[kt][e] = 0u;
-        if (has_head && kt < KT) {
-            const int c = kt * 16 + cq;
-            const bf16* q0 = q + ((size_t)(row0 + r0) * n_heads + head) * hd;
-            const bf16* q1 = q + ((size_t)(row0 + r1) * n_heads + head) * hd;
-            if (r0 < rows && c < hd) qa[kt][0] = *(const uint32_t*)(q0 + c);
-            if (r1 < rows && c < hd) qa[kt][1] = *(const uint32_t*)(q1 + c);
-            if (r0 < rows && c + 8 < hd) qa[kt][2] = *(const uint32_t*)(q0 + c + 8);
-            if (r1 < rows && c + 8 < hd) qa[kt][3] = *(const uint32_t*)(q1 + c + 8);
-        }
-    }
-#pragma unroll
     for (int v = 0; v < VT_MAX; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.0f;
     if (has_head && sink) {
-        m0 = m1 = sink[head];
+        m0 = m1 = sink[head] * LOG2E;
         l0 = l1 = 1.0f;
     }
     const int kvl = has_head ? head / per_kv - kv_lo : 0;
-    __syncthreads();
+    // ldmatrix addresses: a lane's row and column within a 16 x 16 stretch
+    const bf16* q_lane = qs + ((size_t)warp * BM + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + (lane >> 4) * 8;
+    const bf16* k_lane = ks + ((size_t)kvl * BN + (lane & 7) + (lane >> 4) * 8) * KS + ((lane >> 3) & 1) * 8;
+    const bf16* v_lane = vs + ((size_t)kvl * BN + (lane & 7) + ((lane >> 3) & 1) * 8) * VR + (lane >> 4) * 8;
 
     for (int c = 0; c < n_chunks; ++c) {
         const int key0 = key_from + c * BN;
-        // ---- keys as they lie, values transposed (two neighbouring keys of a column in one word) ----
-        {
-            const int ch_k = hd / 8;
-            for (int i = tid; i < nkvl * BN * ch_k; i += THREADS) {
-                const int ch = i % ch_k, r = (i / ch_k) % BN, kv = i / (ch_k * BN);
-                const int key = key0 + r;
-                uint4 val = make_uint4(0u, 0u, 0u, 0u);
-                if (key <= p_last) {
-                    const int page = tab[key / page_tokens];
-                    if (page >= 0)
-                        val = *(const uint4*)(kplane + (((size_t)page * n_kv + kv_lo + kv) * page_tokens + key % page_tokens) * hd + ch * 8);
-                }
-                *(uint4*)(ks + ((size_t)kv * BN + r) * KS + ch * 8) = val;
-            }
-            for (int i = tid; i < nkvl * BN * VT; i += THREADS) {
-                const int r = i % BN, ch = (i / BN) % VT, kv = i / (BN * VT);
-                const int key = key0 + r;
-                uint4 val = make_uint4(0u, 0u, 0u, 0u);
-                if (key <= p_last) {
-                    const int page = tab[key / page_tokens];
-                    if (page >= 0)
-                        val = *(const uint4*)(vplane + (((size_t)page * n_kv + kv_lo + kv) * page_tokens + key % page_tokens) * vd + ch * 8);
-                }
-                const unsigned short* e = (const unsigned short*)&val;
-                unsigned short* dst = (unsigned short*)(vt + ((size_t)kv * vd + ch * 8) * VS + r);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) dst[k * VS] = e[k];
-            }
-        }
+        find_places(c + 1);                                // read from the cluster's meeting below on
+        cp_async_wait<1>();                                // the chunk's keys (and the queries) have arrived; its values may be on the way
         __syncthreads();
         if (c > 0) cluster_wait();                         // every block has read the last chunk's raw scores
 
         // ---- raw scores of this warp's head ----
         if (has_head) {
+            float acc[BN / 8][4];
+#pragma unroll
+            for (int nt = 0; nt < BN / 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+#pragma unroll
+            for (int kt = 0; kt < KT_MAX; ++kt) {
+                if (kt < KT) {
+                    uint32_t a[4], b[4];
+                    ldsm_x4(a, q_lane + kt * 16);
+#pragma unroll
+                    for (int np = 0; np < BN / 16; ++np) {
+                        ldsm_x4(b, k_lane + (size_t)np * 16 * KS + kt * 16);
+                        mma_bf16(acc[2 * np], a, b[0], b[1]);
+                        mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+                    }
+                }
+            }
 #pragma unroll
             for (int nt = 0; nt < BN / 8; ++nt) {
-                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                const bf16* krow = ks + ((size_t)kvl * BN + nt * 8 + r0) * KS + cq;
-#pragma unroll
-                for (int kt = 0; kt < KT_MAX; ++kt)
-                    if (kt < KT) mma_bf16(acc, qa[kt], *(const uint32_t*)(krow + kt * 16), *(const uint32_t*)(krow + kt * 16 + 8));
-                *(float2*)(raw + ((size_t)warp * BM + r0) * RS + nt * 8 + cq) = make_float2(acc[0], acc[1]);
-                *(float2*)(raw + ((size_t)warp * BM + r1) * RS + nt * 8 + cq) = make_float2(acc[2], acc[3]);
+                *(float2*)(raw + ((size_t)warp * BM + r0) * RS + nt * 8 + cq) = make_float2(acc[nt][0], acc[nt][1]);
+                *(float2*)(raw + ((size_t)warp * BM + r1) * RS + nt * 8 + cq) = make_float2(acc[nt][2], acc[nt][3]);
             }
         }
         cluster_arrive();
-        cluster_wait();                                    // all heads' raw scores of the chunk are written
+        cluster_wait();                                    // all heads' raw scores of the chunk are written; the keys are free
+        load_keys(c + 1);                                  // the next chunk's keys travel while this one is mixed and summed
+        cp_async_commit();
 
         // ---- mixing: a thread owns two adjacent keys of a row, and the block's heads ----
         {
@@ -214,22 +256,26 @@ __global__ void __launch_bounds__(THREADS) mixed_heads_tile_kernel(
 #pragma unroll
             for (int u = 0; u < 8; ++u) a[u][0] = a[u][1] = 0.0f;
             for (int rr = 0; rr < C; ++rr) {
-                const float* theirs = cluster.map_shared_rank(raw, rr);
-                for (int gl = 0; gl < HL; ++gl) {
-                    const float2 x = *(const float2*)(theirs + ((size_t)gl * BM + i) * RS + j);
-                    const float4 c0 = *(const float4*)(ct + (size_t)(rr * HL + gl) * 8);
-                    const float4 c1 = *(const float4*)(ct + (size_t)(rr * HL + gl) * 8 + 4);
-                    a[0][0] = fmaf(c0.x, x.x, a[0][0]); a[0][1] = fmaf(c0.x, x.y, a[0][1]);
-                    a[1][0] = fmaf(c0.y, x.x, a[1][0]); a[1][1] = fmaf(c0.y, x.y, a[1][1]);
-                    a[2][0] = fmaf(c0.z, x.x, a[2][0]); a[2][1] = fmaf(c0.z, x.y, a[2][1]);
-                    a[3][0] = fmaf(c0.w, x.x, a[3][0]); a[3][1] = fmaf(c0.w, x.y, a[3][1]);
-                    a[4][0] = fmaf(c1.x, x.x, a[4][0]); a[4][1] = fmaf(c1.x, x.y, a[4][1]);
-                    a[5][0] = fmaf(c1.y, x.x, a[5][0]); a[5][1] = fmaf(c1.y, x.y, a[5][1]);
-                    a[6][0] = fmaf(c1.z, x.x, a[6][0]); a[6][1] = fmaf(c1.z, x.y, a[6][1]);
-                    a[7][0] = fmaf(c1.w, x.x, a[7][0]); a[7][1] = fmaf(c1.w, x.y, a[7][1]);
+                const float* theirs = cluster.map_shared_rank(raw, rr) + (size_t)i * RS + j;
+                float2 x[8];
+#pragma unroll
+                for (int gl = 0; gl < 8; ++gl) x[gl] = gl < HL ? *(const float2*)(theirs + (size_t)gl * BM * RS) : make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (int gl = 0; gl < 8; ++gl) {
+                    if (gl < HL) {
+                        const float4 c0 = *(const float4*)(ct + (size_t)(rr * HL + gl) * 8);
+                        const float4 c1 = *(const float4*)(ct + (size_t)(rr * HL + gl) * 8 + 4);
+                        a[0][0] = fmaf(c0.x, x[gl].x, a[0][0]); a[0][1] = fmaf(c0.x, x[gl].y, a[0][1]);
+                        a[1][0] = fmaf(c0.y, x[gl].x, a[1][0]); a[1][1] = fmaf(c0.y, x[gl].y, a[1][1]);
+                        a[2][0] = fmaf(c0.z, x[gl].x, a[2][0]); a[2][1] = fmaf(c0.z, x[gl].y, a[2][1]);
+                        a[3][0] = fmaf(c0.w, x[gl].x, a[3][0]); a[3][1] = fmaf(c0.w, x[gl].y, a[3][1]);
+                        a[4][0] = fmaf(c1.x, x[gl].x, a[4][0]); a[4][1] = fmaf(c1.x, x[gl].y, a[4][1]);
+                        a[5][0] = fmaf(c1.y, x[gl].x, a[5][0]); a[5][1] = fmaf(c1.y, x[gl].y, a[5][1]);
+                        a[6][0] = fmaf(c1.z, x[gl].x, a[6][0]); a[6][1] = fmaf(c1.z, x[gl].y, a[6][1]);
+                        a[7][0] = fmaf(c1.w, x[gl].x, a[7][0]); a[7][1] = fmaf(c1.w, x[gl].y, a[7][1]);
+                    }
                 }
             }
-            cluster_arrive();                              // done with the other blocks' raw scores
             const int p_i = p0 + min(i, rows - 1);
             const int ka = key0 + j, kb = ka + 1;
             const bool va = ka <= p_i && (window <= 0 || ka > p_i - window);
@@ -238,7 +284,11 @@ __global__ void __launch_bounds__(THREADS) mixed_heads_tile_kernel(
             for (int u = 0; u < 8; ++u)
                 if (u < HL)
                     *(float2*)(mixed + ((size_t)u * BM + i) * RS + j) = make_float2(va ? a[u][0] : -INFINITY, vb ? a[u][1] : -INFINITY);
+            // done with the other blocks' raw scores: what was read has been used, and nothing this block wrote since
+            // the last meeting is for another block to see, so the arrival orders no memory
+            cluster_arrive_relaxed();
         }
+        cp_async_wait<1>();                                // the chunk's values have arrived; the next keys may be on the way
         __syncthreads();
 
         // ---- running softmax and the weighted sum of values of this warp's head ----
@@ -254,12 +304,12 @@ __global__ void __launch_bounds__(THREADS) mixed_heads_tile_kernel(
             }
             const float n0 = fmaxf(m0, quad_max(x0)), n1 = fmaxf(m1, quad_max(x1));
             const float u0 = n0 == -INFINITY ? 0.0f : n0, u1 = n1 == -INFINITY ? 0.0f : n1;   // nothing seen yet: all terms 0
-            const float f0 = expf(m0 - u0), f1 = expf(m1 - u1);
+            const float f0 = exp2f(m0 - u0), f1 = exp2f(m1 - u1);
             float e0 = 0.0f, e1 = 0.0f;
 #pragma unroll
             for (int t = 0; t < BN / 8; ++t) {
-                s0[t].x = expf(s0[t].x - u0); s0[t].y = expf(s0[t].y - u0);
-                s1[t].x = expf(s1[t].x - u1); s1[t].y = expf(s1[t].y - u1);
+                s0[t].x = exp2f(s0[t].x - u0); s0[t].y = exp2f(s0[t].y - u0);
+                s1[t].x = exp2f(s1[t].x - u1); s1[t].y = exp2f(s1[t].y - u1);
                 e0 += s0[t].x + s0[t].y;
                 e1 += s1[t].x + s1[t].y;
             }
@@ -267,28 +317,36 @@ __global__ void __launch_bounds__(THREADS) mixed_heads_tile_kernel(
             l1 = l1 * f1 + quad_sum(e1);
             m0 = n0;
             m1 = n1;
+            if (f0 != 1.0f || f1 != 1.0f) {
 #pragma unroll
-            for (int v = 0; v < VT_MAX; ++v) { o[v][0] *= f0; o[v][1] *= f0; o[v][2] *= f1; o[v][3] *= f1; }
+                for (int v = 0; v < VT_MAX; ++v) { o[v][0] *= f0; o[v][1] *= f0; o[v][2] *= f1; o[v][3] *= f1; }
+            }
 #pragma unroll
             for (int kk = 0; kk < BN / 16; ++kk) {
-                uint32_t hi[4], lo[4];
+                uint32_t hi[4], lo[4], b[4];
                 split_pair(s0[2 * kk].x, s0[2 * kk].y, hi[0], lo[0]);
                 split_pair(s1[2 * kk].x, s1[2 * kk].y, hi[1], lo[1]);
                 split_pair(s0[2 * kk + 1].x, s0[2 * kk + 1].y, hi[2], lo[2]);
                 split_pair(s1[2 * kk + 1].x, s1[2 * kk + 1].y, hi[3], lo[3]);
-                const bf16* vcol = vt + ((size_t)kvl * vd + r0) * VS + kk * 16 + cq;
 #pragma unroll
-                for (int v = 0; v < VT_MAX; ++v) {
+                for (int v = 0; v < VT_MAX; v += 2) {
                     if (v < VT) {
-                        const uint32_t b0 = *(const uint32_t*)(vcol + (size_t)v * 8 * VS), b1 = *(const uint32_t*)(vcol + (size_t)v * 8 * VS + 8);
-                        mma_bf16(o[v], hi, b0, b1);
-                        mma_bf16(o[v], lo, b0, b1);
+                        ldsm_x4_trans(b, v_lane + (size_t)kk * 16 * VR + v * 8);
+                        mma_bf16(o[v], hi, b[0], b[1]);
+                        mma_bf16(o[v], lo, b[0], b[1]);
+                        if (v + 1 < VT) {
+                            mma_bf16(o[v + 1], hi, b[2], b[3]);
+                            mma_bf16(o[v + 1], lo, b[2], b[3]);
+                        }
                     }
                 }
             }
         }
-        __syncthreads();                                   // the chunk's keys, values and mixed scores are free again
+        __syncthreads();                                   // the chunk's values and mixed scores are free again
+        load_values(c + 1);
+        cp_async_commit();
     }
+    cp_async_wait<0>();
     cluster_wait();                                        // no block leaves while another may still read its raw scores
 
     if (has_head) {
@@ -320,8 +378,8 @@ inline size_t tile_smem(int n_heads, int n_kv, int hd, int vd, int C, int& kv_lo
         kv_range(r * HL, HL, per_kv, lo, n);
         if (n > kv_local_max) kv_local_max = n;
     }
-    return (size_t)2 * HL * BM * RS * sizeof(float) + (size_t)n_heads * 8 * sizeof(float) +
-           (size_t)kv_local_max * BN * (hdp + 8) * sizeof(bf16) + (size_t)kv_local_max * vd * VS * sizeof(bf16);
+    return (size_t)2 * HL * BM * RS * sizeof(float) + (size_t)n_heads * 8 * sizeof(float) + (size_t)HL * BM * (hdp + 8) * sizeof(bf16) +
+           (size_t)kv_local_max * BN * (hdp + 8) * sizeof(bf16) + (size_t)kv_local_max * BN * (vd + 8) * sizeof(bf16);
 }
 
 }  // namespace
@@ -350,8 +408,9 @@ CJ_EXPORT int cj_mixed_heads_attention_tile(const void* q, void* out, const void
     if (!cj_mixed_heads_tile_fits(n_heads, n_kv, hd, vd) || page_tokens <= 0) return CJ_ERR_SIZE;
     const int tiles = (total_rows + BM - 1) / BM + n_requests;
     int C = cluster_for(n_heads);
-    // few tiles (single decoded tokens): smaller shares of the heads on more SMs
-    while (C < 8 && n_heads % (2 * C) == 0 && tiles * C < 128) C *= 2;
+    // few tiles (single decoded tokens, a short portion): smaller shares of the heads on more SMs, as long as all
+    // blocks find room at once (two a SM)
+    while (C < 8 && n_heads % (2 * C) == 0 && tiles * C * 2 <= 2 * 148) C *= 2;
     int kvm;
     const size_t smem = tile_smem(n_heads, n_kv, hd, vd, C, kvm);
     static size_t sized = 48 * 1024;

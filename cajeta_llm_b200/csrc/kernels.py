@@ -292,7 +292,7 @@ def mixed_heads_tile_shape(n_heads: int, n_kv: int, head_dim: int, value_dim: in
             hl, per = n_heads // c, n_heads // n_kv
             kv = max((r * hl + hl - 1) // per - (r * hl) // per + 1 for r in range(c))
             hdp = (head_dim + 15) // 16 * 16
-            return 2 * hl * 16 * 40 * 4 + n_heads * 32 + kv * 32 * (hdp + 8) * 2 + kv * value_dim * 40 * 2 <= 200 * 1024
+            return (2 * hl * 16 * 40 * 4 + n_heads * 32 + (hl * 16 + kv * 32) * (hdp + 8) * 2 + kv * 32 * (value_dim + 8) * 2) <= 200 * 1024
     return False
 
 
