@@ -93,7 +93,8 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
     const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ kplane, const bf16* __restrict__ vplane,
     const int* __restrict__ positions, const int* __restrict__ req_start, int n_requests, const int* __restrict__ table,
     int table_stride, int page_tokens, int n_heads, int n_kv, int hd, int vd, int window, float scale,
-    const float* __restrict__ temp, const float* __restrict__ talk, const float* __restrict__ sink, int kv_local_max) {
+    const float* __restrict__ temp, const float* __restrict__ talk, const float* __restrict__ sink, int kv_local_max,
+    float* __restrict__ partial, int total_rows) {
     cj::after_predecessor();
     cj::release_successor();
     cg::cluster_group cluster = cg::this_cluster();
@@ -131,6 +132,10 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
     const int p0 = positions[row0], p_last = p0 + rows - 1;
     const int key_from = (window > 0 && p0 + 1 > window) ? p0 + 1 - window : 0;
     const int n_chunks = (p_last - key_from) / BN + 1;
+    // the keys may be dealt to gridDim.y clusters, a stretch of chunks each: then every one leaves (o, m, l) for the merge
+    const int splits = (int)gridDim.y, split = (int)blockIdx.y;
+    const int per_split = (n_chunks + splits - 1) / splits;
+    const int c_begin = min(n_chunks, split * per_split), c_end = min(n_chunks, c_begin + per_split);
     const int* tab = table + (size_t)req * table_stride;
 
     for (int i = tid; i < n_heads * 8; i += THREADS) {
@@ -155,7 +160,7 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
         if (tid < BN) {
             const int key = key_from + c * BN + tid;
             long long at = -1;
-            if (c < n_chunks && key <= p_last) {
+            if (c < c_end && key <= p_last) {
                 const int page = tab[key / page_tokens];
                 if (page >= 0) at = (long long)page * n_kv * page_tokens + key % page_tokens;
             }
@@ -182,7 +187,7 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
                            vplane + (valid ? ((size_t)at[r] + (size_t)(kv_lo + kv) * page_tokens) * vd + ch * 8 : 0), valid);
             }
     };
-    find_places(0);
+    find_places(c_begin);
     __syncthreads();
     // the tile's queries of this block's heads, then the first chunk's keys, then its values: three groups
     for (int i = tid; i < HL * BM * ch_k; i += THREADS) {
@@ -191,9 +196,9 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
         cp_async16(qs + ((size_t)u * BM + r) * KS + ch * 8, q + ((size_t)(row0 + (valid ? r : 0)) * n_heads + g_lo + u) * hd + ch * 8, valid);
     }
     cp_async_commit();
-    load_keys(0);
+    load_keys(c_begin);
     cp_async_commit();
-    load_values(0);
+    load_values(c_begin);
     cp_async_commit();
 
     // ---- this warp's head: running maximum and sum, output accumulators ----
@@ -203,7 +208,7 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
     for (int v = 0; v < VT_MAX; ++v) o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.0f;
-    if (has_head && sink) {
+    if (has_head && sink && split == 0) {
         m0 = m1 = sink[head] * LOG2E;
         l0 = l1 = 1.0f;
     }
@@ -213,12 +218,12 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
     const bf16* k_lane = ks + ((size_t)kvl * BN + (lane & 7) + (lane >> 4) * 8) * KS + ((lane >> 3) & 1) * 8;
     const bf16* v_lane = vs + ((size_t)kvl * BN + (lane & 7) + ((lane >> 3) & 1) * 8) * VR + (lane >> 4) * 8;
 
-    for (int c = 0; c < n_chunks; ++c) {
+    for (int c = c_begin; c < c_end; ++c) {
         const int key0 = key_from + c * BN;
         find_places(c + 1);                                // read from the cluster's meeting below on
         cp_async_wait<1>();                                // the chunk's keys (and the queries) have arrived; its values may be on the way
         __syncthreads();
-        if (c > 0) cluster_wait();                         // every block has read the last chunk's raw scores
+        if (c > c_begin) cluster_wait();                         // every block has read the last chunk's raw scores
 
         // ---- raw scores of this warp's head ----
         if (has_head) {
@@ -347,7 +352,27 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
         cp_async_commit();
     }
     cp_async_wait<0>();
-    cluster_wait();                                        // no block leaves while another may still read its raw scores
+    if (c_end > c_begin) cluster_wait();                   // no block leaves while another may still read its raw scores
+
+    if (partial) {
+        // [split][row][head][vd + 2]: the sum of weighted values as it stands, then the maximum (in units of log 2) and the sum
+        if (has_head) {
+            float* d0 = partial + (((size_t)split * total_rows + row0 + r0) * n_heads + head) * (vd + 2);
+            float* d1 = partial + (((size_t)split * total_rows + row0 + r1) * n_heads + head) * (vd + 2);
+#pragma unroll
+            for (int v = 0; v < VT_MAX; ++v) {
+                if (v < VT) {
+                    if (r0 < rows) *(float2*)(d0 + v * 8 + cq) = make_float2(o[v][0], o[v][1]);
+                    if (r1 < rows) *(float2*)(d1 + v * 8 + cq) = make_float2(o[v][2], o[v][3]);
+                }
+            }
+            if ((lane & 3) == 0) {
+                if (r0 < rows) { d0[vd] = m0; d0[vd + 1] = l0; }
+                if (r1 < rows) { d1[vd] = m1; d1[vd + 1] = l1; }
+            }
+        }
+        return;
+    }
 
     if (has_head) {
         const float i0 = 1.0f / l0, i1 = 1.0f / l1;
@@ -360,6 +385,33 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
                 if (r1 < rows) *(__nv_bfloat162*)(o1 + v * 8) = __floats2bfloat162_rn(o[v][2] * i1, o[v][3] * i1);
             }
         }
+    }
+}
+
+// One warp a (row, head): the clusters' shares of the keys are put together, o = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s.
+__global__ void __launch_bounds__(128) mixed_heads_merge_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits,
+                                                                int total_rows, int n_heads, int vd) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5);                 // row * n_heads + head
+    if (item >= total_rows * n_heads) return;
+    const size_t each = (size_t)total_rows * n_heads * (vd + 2);
+    const float* p = partial + (size_t)item * (vd + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * each + vd]);
+    float L = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float m = p[s * each + vd];
+        if (m != -INFINITY) L = fmaf(p[s * each + vd + 1], exp2f(m - M), L);
+    }
+    for (int d = lane; d < vd; d += 32) {
+        float a = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float m = p[s * each + vd];
+            if (m != -INFINITY) a = fmaf(p[s * each + d], exp2f(m - M), a);
+        }
+        out[(size_t)item * vd + d] = __float2bfloat16_rn(a / L);
     }
 }
 
@@ -398,19 +450,24 @@ CJ_EXPORT int cj_mixed_heads_tile_fits(int n_heads, int n_kv, int hd, int vd) {
 
 // q [T, n_heads, hd], out [T, n_heads, vd], planes [pages, n_kv, page_tokens, hd | vd]: bfloat16.  req_start
 // [n_requests + 1]: the rows of request r are [req_start[r], req_start[r + 1]), at consecutive positions.
-// temp [n_heads], talk [n_heads, n_heads], sink [n_heads]: float32 or null.
+// temp [n_heads], talk [n_heads, n_heads], sink [n_heads]: float32 or null.  cluster_blocks: 0 = chosen here, else the cluster's
+// size (a power of two up to 8 that divides n_heads and leaves a block at most 8 heads).  splits > 1: a tile's chunks of keys are
+// dealt to that many clusters, which leave their shares in partial, float32 [splits, total_rows, n_heads, vd + 2], and a second
+// kernel puts them together: for steps of few rows (single decoded tokens), where a tile's chunks would run one after the other.
 CJ_EXPORT int cj_mixed_heads_attention_tile(const void* q, void* out, const void* kplane, const void* vplane, const int* positions,
                                             const int* req_start, int n_requests, int total_rows, const int* table, int table_stride,
                                             int page_tokens, int n_heads, int n_kv, int hd, int vd, int window, float scale,
-                                            const float* temp, const float* talk, const float* sink, cudaStream_t stream) {
+                                            const float* temp, const float* talk, const float* sink, int cluster_blocks, float* partial, int splits,
+                                            cudaStream_t stream) {
     if (total_rows <= 0 || n_requests <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !positions || !req_start || !table) return CJ_ERR_ARG;
     if (!cj_mixed_heads_tile_fits(n_heads, n_kv, hd, vd) || page_tokens <= 0) return CJ_ERR_SIZE;
     const int tiles = (total_rows + BM - 1) / BM + n_requests;
     int C = cluster_for(n_heads);
-    // few tiles (single decoded tokens, a short portion): smaller shares of the heads on more SMs, as long as all
-    // blocks find room at once (two a SM)
-    while (C < 8 && n_heads % (2 * C) == 0 && tiles * C * 2 <= 2 * 148) C *= 2;
+    if (cluster_blocks > 0) {
+        if ((cluster_blocks & (cluster_blocks - 1)) || cluster_blocks > 8 || n_heads % cluster_blocks || n_heads / cluster_blocks > WARPS) return CJ_ERR_SIZE;
+        C = cluster_blocks;
+    }
     int kvm;
     const size_t smem = tile_smem(n_heads, n_kv, hd, vd, C, kvm);
     static size_t sized = 48 * 1024;
@@ -420,7 +477,8 @@ CJ_EXPORT int cj_mixed_heads_attention_tile(const void* q, void* out, const void
         sized = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles * C);
+    if (splits < 1 || (splits > 1 && !partial)) return CJ_ERR_ARG;
+    cfg.gridDim = dim3(tiles * C, splits);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -433,6 +491,9 @@ CJ_EXPORT int cj_mixed_heads_attention_tile(const void* q, void* out, const void
     cfg.numAttrs = 1;
     cudaLaunchKernelEx(&cfg, mixed_heads_tile_kernel, (const bf16*)q, (bf16*)out, (const bf16*)kplane, (const bf16*)vplane, positions,
                        req_start, n_requests, table, table_stride, page_tokens, n_heads, n_kv, hd, vd, window, scale, temp, talk,
-                       sink, kvm);
+                       sink, kvm, splits > 1 ? partial : (float*)nullptr, total_rows);
+    if (splits > 1)
+        cj::launch(mixed_heads_merge_kernel, dim3((total_rows * n_heads + 3) / 4), dim3(128), 0, stream, (const float*)partial, (bf16*)out,
+                   splits, total_rows, n_heads, vd);
     return launch_status();
 }

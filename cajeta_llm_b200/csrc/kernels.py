@@ -279,6 +279,16 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v
     _check(st, "paged_attention")
 
 
+_sms: Dict[int, int] = {}
+
+
+def _sm_count() -> int:
+    d = torch.cuda.current_device()
+    if d not in _sms:
+        _sms[d] = int(torch.cuda.get_device_properties(d).multi_processor_count)
+    return _sms[d]
+
+
 def mixed_heads_tile_shape(n_heads: int, n_kv: int, head_dim: int, value_dim: int) -> bool:
     """Whether the tiled form of the mixed-heads attention takes these sizes: head and value sizes multiples of 8 up
     to 128, and heads that 1, 2, 4 or 8 blocks share out evenly, at most 8 a block.  A matter of arithmetic: the
@@ -301,7 +311,7 @@ def mixed_heads_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Ten
                           n_heads: int, n_kv: int, head_dim: int, value_dim: int, window: int, scale: float,
                           temp: Optional[torch.Tensor] = None, talk: Optional[torch.Tensor] = None,
                           sink: Optional[torch.Tensor] = None, req_start: Optional[torch.Tensor] = None,
-                          n_requests: int = 0) -> None:
+                          n_requests: int = 0, cluster_blocks: int = 0, splits: Optional[int] = None) -> None:
     """Attention of every row over its request's cached keys [from, position] in which the heads' scores are mixed
     before the softmax: raw_g = (q_g . k) scale temp[g]; s_h = sum_g talk[h, g] raw_g; the softmax's divisor also
     holds exp(sink[h]).  ``temp`` [heads], ``talk`` [heads, heads], ``sink`` [heads]: float32, each optional.
@@ -318,10 +328,21 @@ def mixed_heads_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Ten
     if (req_start is not None and n_requests > 0 and q.dtype == torch.bfloat16 and k_plane.dtype == torch.bfloat16
             and mixed_heads_tile_shape(n_heads, n_kv, head_dim, value_dim or head_dim)):
         _need(req_start, "req_start", torch.int32)
+        vd = value_dim or head_dim
+        T = q.shape[0]
+        # few tiles (single decoded tokens, a short portion): a tile's chunks of keys are dealt to several clusters, as many
+        # as still find room on the SMs at once (two blocks a SM), and put together by a second kernel
+        tiles = (T + 15) // 16 + n_requests
+        c = next(c for c in (1, 2, 4, 8) if n_heads % c == 0 and n_heads // c <= 8)
+        if splits is None:
+            splits = max(1, min(8, (2 * _sm_count()) // (tiles * max(c, cluster_blocks))))
+            if window > 0:
+                splits = min(splits, max(1, (window + 46) // 64))      # at least two chunks of 32 keys a share
+        partial = torch.empty((splits, T, n_heads, vd + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
         st = library("attention_mixed").cj_mixed_heads_attention_tile(
-            _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(positions), _ptr(req_start), _i(n_requests), _i(q.shape[0]),
-            _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_heads), _i(n_kv), _i(head_dim), _i(value_dim or head_dim),
-            _i(window), _f(scale), _ptr(temp), _ptr(talk), _ptr(sink), _stream())
+            _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(positions), _ptr(req_start), _i(n_requests), _i(T),
+            _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_heads), _i(n_kv), _i(head_dim), _i(vd),
+            _i(window), _f(scale), _ptr(temp), _ptr(talk), _ptr(sink), _i(cluster_blocks), _ptr(partial), _i(splits), _stream())
         _check(st, "mixed_heads_attention (tiled)")
         return
     st = library("attention_paged").cj_mixed_heads_attention(

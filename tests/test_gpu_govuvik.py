@@ -558,13 +558,19 @@ def test_tiled_mixed_heads_attention_against_the_formula(H, G, hd, vd, window, r
     sink = torch.randn(H, generator=g)
     scale = hd ** -0.5
     want = _mixed_attention_formula(q, keys, values, positions, row_req, window, scale, temp, talk, sink)
-    got = torch.full((q.shape[0], H, vd), float("nan"), dtype=torch.bfloat16, device=dev)
-    K.mixed_heads_attention(q.to(dev), got, kp.to(dev), vp.to(dev), positions.to(dev), row_req.to(dev), table.to(dev), page, H, G, hd,
-                            vd, window, scale, temp=temp.to(dev), talk=talk.to(dev), sink=sink.to(dev),
-                            req_start=torch.tensor(starts, dtype=torch.int32, device=dev), n_requests=len(requests))
-    assert "attention_mixed" in K.loaded_libraries()
-    err = (got.cpu().double() - want).abs()
-    assert float(err.max()) < 0.01 * max(1.0, float(want.abs().max())), f"row {int(err.amax(dim=(1, 2)).argmax())} differs by {float(err.max()):.3g}"
+    # the cluster's size and the number of clusters a tile's keys are dealt to, chosen by the library and given
+    largest = max(c for c in (1, 2, 4, 8) if H % c == 0 and H // c <= 8)
+    smallest = min(c for c in (1, 2, 4, 8) if H % c == 0 and H // c <= 8)
+    for blocks, splits in ((0, None), (smallest, 1), (largest, 3), (0, 8)):
+        got = torch.full((q.shape[0], H, vd), float("nan"), dtype=torch.bfloat16, device=dev)
+        K.mixed_heads_attention(q.to(dev), got, kp.to(dev), vp.to(dev), positions.to(dev), row_req.to(dev), table.to(dev), page, H, G, hd,
+                                vd, window, scale, temp=temp.to(dev), talk=talk.to(dev), sink=sink.to(dev),
+                                req_start=torch.tensor(starts, dtype=torch.int32, device=dev), n_requests=len(requests),
+                                cluster_blocks=blocks, splits=splits)
+        assert "attention_mixed" in K.loaded_libraries()
+        err = (got.cpu().double() - want).abs()
+        assert float(err.max()) < 0.01 * max(1.0, float(want.abs().max())), \
+            f"cluster of {blocks}, {splits} shares: row {int(err.amax(dim=(1, 2)).argmax())} differs by {float(err.max()):.3g}"
     if window > 0:
         # the same rows with the window one key longer and one key shorter differ by far more than that
         for other in (window + 1, max(1, window - 1)):
