@@ -65,19 +65,19 @@ GOVUVIK_WINDOW = 1024
 
 
 def govuvik_config(s):
-    """Four layers: matrix memory, two layers of windowed attention with mixed heads beside gated linear attention,
-    matrix memory; every layer with a routed feed-forward of ungated experts."""
+    """Four layers: windowed attention with mixed heads beside gated linear attention, matrix memory, and the two once more;
+    every layer with a routed feed-forward of ungated experts."""
     h, H = s["width"], s["heads"]
-    memory = {"heads": H // 2, "dim": 128, "vdim": 256, "gate_cap": 15.0}
+    memory = {"heads": H // 2, "dim": 128, "vdim": 256, "gate_cap": 10.0}
     left = {"conv": 4, "dim": 128, "heads": H, "kv_heads": H // 4, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": GOVUVIK_WINDOW},
-            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
-    right = {"heads": H // 4, "dim": 128, "vdim": 256, "tau": 16.0, "decay_rank": 16}
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 8192}}}
+    right = {"heads": H // 4, "dim": 128, "vdim": 256, "tau": 8.0, "decay_rank": 16}
     moe = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
-    kinds = [lambda: {"type": "mlstm", "mixer": dict(memory), "mlp": moe},
-             lambda: {"type": "parallel", "mixer": {"left": dict(left), "right": dict(right)}, "mlp": moe},
+    kinds = [lambda: {"type": "parallel", "mixer": {"left": dict(left), "right": dict(right)}, "mlp": moe},
+             lambda: {"type": "mlstm", "mixer": dict(memory), "mlp": moe},
              lambda: {"type": "parallel", "mixer": {"left": dict(left), "right": dict(right)}, "mlp": moe},
              lambda: {"type": "mlstm", "mixer": dict(memory), "mlp": moe}]
-    return {"architecture": "Govuvik", "width": h, "vocab": VOCAB, "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "logit_softcap": 30.0,
+    return {"architecture": "Govuvik", "width": h, "vocab": VOCAB, "norm": {"eps": 1e-6}, "canon": {"taps": 3}, "logit_softcap": 50.0,
             "layers": [kinds[i % 4]() for i in range(s["layers"])]}
 
 
@@ -107,7 +107,7 @@ def needs(design, s, rows, ctx, prefill):
         out["attention"] = (by, fl)
         return out
     if design == "govuvik":
-        n_mem, n_par = (L + 3) // 4 + L // 4, (L + 2) // 4 + (L + 1) // 4
+        n_par, n_mem = (L + 3) // 4 + (L + 1) // 4, (L + 2) // 4 + L // 4
         w = GOVUVIK_WINDOW
         out["attention"] = (rows * min(ctx, w) * 2 * (H // 4) * 128 * 2 * n_par if not prefill else 0,
                             4 * H * 128 * sum(min(i + 1, w) for i in range(rows)) * n_par if prefill else 0)

@@ -56,6 +56,12 @@ __device__ __forceinline__ void split_pair(float x, float y, uint32_t& hi, uint3
     const __nv_bfloat162 l = __floats2bfloat162_rn(x - __uint_as_float(hi << 16), y - __uint_as_float(hi & 0xffff0000u));
     lo = *(const uint32_t*)&l;
 }
+// 2^x by the special-function unit alone (relative error about 2^-22; -inf gives 0)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float quad_max(float v) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
     return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -89,17 +95,20 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
 }
 
+// FULL: heads and values of 128 and 8 heads a block, known to the compiler: the generic loops' guards fall away.
+template <bool FULL>
 __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
     const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ kplane, const bf16* __restrict__ vplane,
     const int* __restrict__ positions, const int* __restrict__ req_start, int n_requests, const int* __restrict__ table,
-    int table_stride, int page_tokens, int n_heads, int n_kv, int hd, int vd, int window, float scale,
+    int table_stride, int page_tokens, int n_heads, int n_kv, int hd_given, int vd_given, int window, float scale,
     const float* __restrict__ temp, const float* __restrict__ talk, const float* __restrict__ sink, int kv_local_max,
     float* __restrict__ partial, int total_rows) {
     cj::after_predecessor();
     cj::release_successor();
     cg::cluster_group cluster = cg::this_cluster();
     const int C = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
-    const int HL = n_heads / C, g_lo = crank * HL, per_kv = n_heads / n_kv;
+    const int hd = FULL ? 128 : hd_given, vd = FULL ? 128 : vd_given;
+    const int HL = FULL ? WARPS : n_heads / C, g_lo = crank * HL, per_kv = n_heads / n_kv;
     int kv_lo, nkvl;
     kv_range(g_lo, HL, per_kv, kv_lo, nkvl);
     const int hdp = (hd + 15) & ~15, KT = hdp / 16, VT = vd / 8, KS = hdp + 8, VR = vd + 8;
@@ -257,9 +266,9 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
         // ---- mixing: a thread owns two adjacent keys of a row, and the block's heads ----
         {
             const int i = tid >> 4, j = (tid & 15) * 2;
-            float a[8][2];
+            float2 a[8];                                   // packed: one instruction multiplies a coefficient into both keys
 #pragma unroll
-            for (int u = 0; u < 8; ++u) a[u][0] = a[u][1] = 0.0f;
+            for (int u = 0; u < 8; ++u) a[u] = make_float2(0.0f, 0.0f);
             for (int rr = 0; rr < C; ++rr) {
                 const float* theirs = cluster.map_shared_rank(raw, rr) + (size_t)i * RS + j;
                 float2 x[8];
@@ -270,14 +279,14 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
                     if (gl < HL) {
                         const float4 c0 = *(const float4*)(ct + (size_t)(rr * HL + gl) * 8);
                         const float4 c1 = *(const float4*)(ct + (size_t)(rr * HL + gl) * 8 + 4);
-                        a[0][0] = fmaf(c0.x, x[gl].x, a[0][0]); a[0][1] = fmaf(c0.x, x[gl].y, a[0][1]);
-                        a[1][0] = fmaf(c0.y, x[gl].x, a[1][0]); a[1][1] = fmaf(c0.y, x[gl].y, a[1][1]);
-                        a[2][0] = fmaf(c0.z, x[gl].x, a[2][0]); a[2][1] = fmaf(c0.z, x[gl].y, a[2][1]);
-                        a[3][0] = fmaf(c0.w, x[gl].x, a[3][0]); a[3][1] = fmaf(c0.w, x[gl].y, a[3][1]);
-                        a[4][0] = fmaf(c1.x, x[gl].x, a[4][0]); a[4][1] = fmaf(c1.x, x[gl].y, a[4][1]);
-                        a[5][0] = fmaf(c1.y, x[gl].x, a[5][0]); a[5][1] = fmaf(c1.y, x[gl].y, a[5][1]);
-                        a[6][0] = fmaf(c1.z, x[gl].x, a[6][0]); a[6][1] = fmaf(c1.z, x[gl].y, a[6][1]);
-                        a[7][0] = fmaf(c1.w, x[gl].x, a[7][0]); a[7][1] = fmaf(c1.w, x[gl].y, a[7][1]);
+                        a[0] = __ffma2_rn(make_float2(c0.x, c0.x), x[gl], a[0]);
+                        a[1] = __ffma2_rn(make_float2(c0.y, c0.y), x[gl], a[1]);
+                        a[2] = __ffma2_rn(make_float2(c0.z, c0.z), x[gl], a[2]);
+                        a[3] = __ffma2_rn(make_float2(c0.w, c0.w), x[gl], a[3]);
+                        a[4] = __ffma2_rn(make_float2(c1.x, c1.x), x[gl], a[4]);
+                        a[5] = __ffma2_rn(make_float2(c1.y, c1.y), x[gl], a[5]);
+                        a[6] = __ffma2_rn(make_float2(c1.z, c1.z), x[gl], a[6]);
+                        a[7] = __ffma2_rn(make_float2(c1.w, c1.w), x[gl], a[7]);
                     }
                 }
             }
@@ -288,7 +297,7 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
 #pragma unroll
             for (int u = 0; u < 8; ++u)
                 if (u < HL)
-                    *(float2*)(mixed + ((size_t)u * BM + i) * RS + j) = make_float2(va ? a[u][0] : -INFINITY, vb ? a[u][1] : -INFINITY);
+                    *(float2*)(mixed + ((size_t)u * BM + i) * RS + j) = make_float2(va ? a[u].x : -INFINITY, vb ? a[u].y : -INFINITY);
             // done with the other blocks' raw scores: what was read has been used, and nothing this block wrote since
             // the last meeting is for another block to see, so the arrival orders no memory
             cluster_arrive_relaxed();
@@ -309,12 +318,12 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
             }
             const float n0 = fmaxf(m0, quad_max(x0)), n1 = fmaxf(m1, quad_max(x1));
             const float u0 = n0 == -INFINITY ? 0.0f : n0, u1 = n1 == -INFINITY ? 0.0f : n1;   // nothing seen yet: all terms 0
-            const float f0 = exp2f(m0 - u0), f1 = exp2f(m1 - u1);
+            const float f0 = ex2(m0 - u0), f1 = ex2(m1 - u1);
             float e0 = 0.0f, e1 = 0.0f;
 #pragma unroll
             for (int t = 0; t < BN / 8; ++t) {
-                s0[t].x = exp2f(s0[t].x - u0); s0[t].y = exp2f(s0[t].y - u0);
-                s1[t].x = exp2f(s1[t].x - u1); s1[t].y = exp2f(s1[t].y - u1);
+                s0[t].x = ex2(s0[t].x - u0); s0[t].y = ex2(s0[t].y - u0);
+                s1[t].x = ex2(s1[t].x - u1); s1[t].y = ex2(s1[t].y - u1);
                 e0 += s0[t].x + s0[t].y;
                 e1 += s1[t].x + s1[t].y;
             }
@@ -472,7 +481,8 @@ CJ_EXPORT int cj_mixed_heads_attention_tile(const void* q, void* out, const void
     const size_t smem = tile_smem(n_heads, n_kv, hd, vd, C, kvm);
     static size_t sized = 48 * 1024;
     if (smem > sized) {
-        cudaError_t e = cudaFuncSetAttribute(mixed_heads_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(mixed_heads_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(mixed_heads_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         sized = smem;
     }
@@ -489,9 +499,10 @@ CJ_EXPORT int cj_mixed_heads_attention_tile(const void* q, void* out, const void
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, mixed_heads_tile_kernel, (const bf16*)q, (bf16*)out, (const bf16*)kplane, (const bf16*)vplane, positions,
-                       req_start, n_requests, table, table_stride, page_tokens, n_heads, n_kv, hd, vd, window, scale, temp, talk,
-                       sink, kvm, splits > 1 ? partial : (float*)nullptr, total_rows);
+    const bool full = hd == 128 && vd == 128 && n_heads / C == WARPS;
+    cudaLaunchKernelEx(&cfg, full ? mixed_heads_tile_kernel<true> : mixed_heads_tile_kernel<false>, (const bf16*)q, (bf16*)out,
+                       (const bf16*)kplane, (const bf16*)vplane, positions, req_start, n_requests, table, table_stride, page_tokens,
+                       n_heads, n_kv, hd, vd, window, scale, temp, talk, sink, kvm, splits > 1 ? partial : (float*)nullptr, total_rows);
     if (splits > 1)
         cj::launch(mixed_heads_merge_kernel, dim3((total_rows * n_heads + 3) / 4), dim3(128), 0, stream, (const float*)partial, (bf16*)out,
                    splits, total_rows, n_heads, vd);
