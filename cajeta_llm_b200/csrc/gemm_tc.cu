@@ -40,7 +40,8 @@ constexpr int UMMA_K = 16;         // K of one tcgen05.mma of kind::f16
 constexpr int THREADS = 224;          // warps 0 and 6: loads; warp 1: products; warps 2-5: epilogue
 constexpr int LOADERS = 2;
 
-enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3 };
+// EPI_RELU2_BF16: max(v, 0)^2 of the float32 sum (bias included), rounded to bfloat16: an expert without a gate
+enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3, EPI_RELU2_BF16 = 4 };
 
 struct Args {
     int tokens;                 // rows of X
@@ -379,6 +380,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j) if (whole || feat + j < p.features) v[j] += p.bias[feat + j];
                     }
+                    if (EPI == EPI_RELU2_BF16) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) { const float t = fmaxf(v[j], 0.0f); v[j] = t * t; }
+                    }
                     if (EPI == EPI_STORE_F32 || EPI == EPI_ACC_F32) {
                         float* dst = (float*)p.out + o + (EPI == EPI_STORE_F32 ? split_off : 0);
                         if (whole && (((uintptr_t)dst) & 15) == 0) {
@@ -425,6 +430,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         if (token >= c.tok_end) break;
                         long long o = (long long)token * p.ldo + feat;
                         float val = v[j] + b;
+                        if (EPI == EPI_RELU2_BF16) { val = fmaxf(val, 0.0f); val *= val; }
                         if (EPI == EPI_STORE_F32) ((float*)p.out)[o + split_off] = val;
                         else if (EPI == EPI_ACC_F32) ((float*)p.out)[o] += val;
                         else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
@@ -573,6 +579,7 @@ CJ_EXPORT int cj_gemm_tc(const void* x, long long ldx, const void* w, const void
         case EPI_ACC_F32: CASE(EPI_ACC_F32, false)
         case EPI_SWIGLU_BF16: CASE(EPI_SWIGLU_BF16, true)
         case EPI_STORE_BF16: CASE(EPI_STORE_BF16, false)
+        case EPI_RELU2_BF16: CASE(EPI_RELU2_BF16, false)
     }
 #undef CASE
     return CJ_ERR_ARG;

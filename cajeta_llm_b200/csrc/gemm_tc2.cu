@@ -46,7 +46,7 @@ constexpr int FEAT_TILE = 256;      // feature rows a pair of blocks covers
 constexpr int MAX_GROUPS = 1024;
 constexpr int MAX_ACC_STAGES = 2;
 
-enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3 };
+enum Epilogue { EPI_STORE_F32 = 0, EPI_ACC_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_BF16 = 3, EPI_RELU2_BF16 = 4 };
 
 struct Args {
     int tokens, features, K;
@@ -267,6 +267,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         for (int j = 0; j < 32; ++j) {
                             if (c0 + j >= n_cols) break;
                             float val = __uint_as_float(v[j]) + b;
+                            if (EPI == EPI_RELU2_BF16) { val = fmaxf(val, 0.0f); val *= val; }       // an expert without a gate
                             if (EPI == EPI_STORE_F32) ((float*)p.out)[o0 + j * p.ldo] = val;
                             else ((__nv_bfloat16*)p.out)[o0 + j * p.ldo] = __float2bfloat16_rn(val);
                         }
@@ -582,6 +583,7 @@ CJ_EXPORT int cj_gemm_tc2(const void* x, long long ldx, const void* w, const voi
         case EPI_STORE_F32: CASE(EPI_STORE_F32)
         case EPI_ACC_F32: CASE(EPI_ACC_F32)
         case EPI_STORE_BF16: CASE(EPI_STORE_BF16)
+        case EPI_RELU2_BF16: CASE(EPI_RELU2_BF16)
     }
 #undef CASE
     return CJ_ERR_ARG;

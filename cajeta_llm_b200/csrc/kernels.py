@@ -885,7 +885,7 @@ def random_fill(out: torch.Tensor, key: int, scale: float) -> None:
     _check(st, "random_fill")
 
 
-EPI_STORE_F32, EPI_ACC_F32, EPI_SWIGLU_BF16, EPI_STORE_BF16 = 0, 1, 2, 3
+EPI_STORE_F32, EPI_ACC_F32, EPI_SWIGLU_BF16, EPI_STORE_BF16, EPI_RELU2_BF16 = 0, 1, 2, 3, 4
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, swap: bool, n_mma: int,
@@ -897,7 +897,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
 
     ``swap`` False: tiles of 128 tokens x ``n_mma`` (128 or 256) features; True: tiles of 128
     features x ``n_mma`` (16, 32, 64, 96, 128, 160, 192, 256) tokens.  ``epilogue``: EPI_STORE_F32, EPI_ACC_F32,
-    EPI_SWIGLU_BF16 (``w_up`` given), EPI_STORE_BF16.  With ``group_offsets`` the rows of
+    EPI_SWIGLU_BF16 (``w_up`` given), EPI_STORE_BF16, EPI_RELU2_BF16 (``max(sum, 0)^2`` rounded to bfloat16).  With ``group_offsets`` the rows of
     ``x`` are sorted by group and ``w`` is [groups, features, K].  ``k_splits`` > 1 (store
     only): ``out`` is [k_splits, tokens, features] of partial sums.  ``offsets_settled``: the
     kernel that wrote ``group_offsets`` is not the one launched just before this product but an
@@ -908,7 +908,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     T = tokens if tokens is not None else x.shape[0]
     if x.shape[-1] != K or out.shape[-1] != features:
         raise KernelError(f"gemm_tc: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)} do not agree")
-    want = torch.bfloat16 if epilogue in (EPI_SWIGLU_BF16, EPI_STORE_BF16) else torch.float32
+    want = torch.bfloat16 if epilogue in (EPI_SWIGLU_BF16, EPI_STORE_BF16, EPI_RELU2_BF16) else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm_tc: epilogue {epilogue} writes {want}, out is {out.dtype}")
     if w_up is not None:
@@ -940,7 +940,7 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
     T = tokens if tokens is not None else x.shape[0]
     if x.shape[-1] != K or out.shape[-1] != features:
         raise KernelError(f"gemm_tc2: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)} do not agree")
-    want = torch.bfloat16 if epilogue in (EPI_SWIGLU_BF16, EPI_STORE_BF16) else torch.float32
+    want = torch.bfloat16 if epilogue in (EPI_SWIGLU_BF16, EPI_STORE_BF16, EPI_RELU2_BF16) else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm_tc2: epilogue {epilogue} writes {want}, out is {out.dtype}")
     if w_up is not None:

@@ -48,7 +48,7 @@ import torch
 
 from ..csrc import kernels as K
 from .base import Part, register_part
-from .linear import project
+from .linear import project, relu2_fused
 from .plan import ParamSpec
 
 
@@ -316,8 +316,12 @@ class SparseMoE(Part):
             project(rt, scaled, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, max_group_rows=T,
                     offsets_settled=True, act_limit=self.act_limit, act_alpha=self.act_alpha)
             wts = torch.ones_like(wts)
+        elif not self.gated and relu2_fused(rt, x, self.w_up, act.dtype):
+            # an expert without a gate: the rectified float32 sum is squared in the product's epilogue, then rounded
+            K.tag = "experts up"
+            project(rt, x, self.w_up[:G], act, group_offsets=offsets, a_row_index=slot_token, max_group_rows=T, relu2=True)
         elif not self.gated:
-            # an expert without a gate: the product in float32, then the activation as it is rounded
+            # the float32 path: the product, then the activation, as two kernels
             pre = torch.empty((n_slots, self.inter), dtype=torch.float32, device=dev)
             K.tag = "experts up"
             project(rt, x, self.w_up[:G], pre, group_offsets=offsets, a_row_index=slot_token, max_group_rows=T)

@@ -79,7 +79,7 @@ def _pair_tile(runtime, rows: int, w: torch.Tensor, swiglu: bool, grouped: bool)
 def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
             accumulate: bool = False, w_up: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
             a_row_index: Optional[torch.Tensor] = None, max_group_rows: Optional[int] = None,
-            offsets_settled: bool = False, act_limit: float = 0.0, act_alpha: float = 1.0) -> None:
+            offsets_settled: bool = False, act_limit: float = 0.0, act_alpha: float = 1.0, relu2: bool = False) -> None:
     """``x``: [tokens, K]; ``w``: [features, K] or, with ``group_offsets``, [groups, features, K]
     where output row s belongs to the group whose range holds s and reads row
     ``a_row_index[s]`` of ``x`` (or row s).  ``w_up`` selects the SwiGLU form (``out`` in the
@@ -88,7 +88,10 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
     before this call's product (another kernel of this engine ran since, or this call's own
     row gather does); the product may then read the offsets before it waits for that kernel.
     ``act_limit`` > 0 (with ``w_up``): the capped gate g = min(g, limit), u = clamp(u, +-limit),
-    g * sigmoid(act_alpha g) * (u + 1) instead of silu(g) * u."""
+    g * sigmoid(act_alpha g) * (u + 1) instead of silu(g) * u.  ``relu2`` (tensor-core path, ``out`` bfloat16, no ``w_up``):
+    ``out = max(x w^T, 0)^2``, the float32 sum squared before it is rounded; ask :func:`relu2_fused` first."""
+    if relu2 and (w_up is not None or out.dtype != torch.bfloat16 or not _tc_ok(runtime, x, w)):
+        raise ValueError("project: relu2 is the tensor-core product's epilogue (bfloat16 out, no second weight)")
     if not _tc_ok(runtime, x, w):
         K.gemm(x, w, out, bias=bias, accumulate=accumulate, w_up=w_up, group_offsets=group_offsets, a_row_index=a_row_index,
                act_limit=act_limit, act_alpha=act_alpha)
@@ -97,7 +100,7 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
     if w_up is not None:
         epi = K.EPI_SWIGLU_BF16
     elif out.dtype == torch.bfloat16:
-        epi = K.EPI_STORE_BF16
+        epi = K.EPI_RELU2_BF16 if relu2 else K.EPI_STORE_BF16
     else:
         epi = K.EPI_ACC_F32 if accumulate else K.EPI_STORE_F32
     bound = rows if max_group_rows is None else min(rows, max_group_rows)
@@ -130,6 +133,11 @@ def project(runtime, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bia
         n_mma = 256 if (w_up is None and w.shape[-2] >= 512) else 128
         K.gemm_tc(x, w, out, epi, False, n_mma, bias=bias, w_up=w_up, group_offsets=group_offsets, tokens=rows,
                   offsets_settled=offsets_settled, act_limit=act_limit, act_alpha=act_alpha)
+
+
+def relu2_fused(runtime, x: torch.Tensor, w: torch.Tensor, out_dtype) -> bool:
+    """Whether :func:`project` can square the rectified sum in its own epilogue for these operands."""
+    return out_dtype == torch.bfloat16 and _tc_ok(runtime, x, w)
 
 
 def project_split(runtime, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:

@@ -47,6 +47,9 @@ def test_store_accumulate_bias(K, swap, n_mma, T, N, Kd):
     ob = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
     K.gemm_tc(x, w, ob, K.EPI_STORE_BF16, swap, n_mma)
     close(ob, want, atol=2e-2, rtol=1e-2)
+    # the rectified sum (bias included) squared before it is rounded
+    K.gemm_tc(x, w, ob, K.EPI_RELU2_BF16, swap, n_mma, bias=bias)
+    close(ob, (want + bias.double()).clamp(min=0.0) ** 2, atol=4e-2, rtol=1e-2)
 
 
 @pytest.mark.parametrize("swap,n_mma,T", [(False, 128, 200), (True, 16, 9), (True, 64, 50)])
@@ -240,6 +243,8 @@ def test_pair_product_dense(K, n_tok):
     ob = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
     K.gemm_tc2(x, w, ob, K.EPI_STORE_BF16, n_tok)
     close(ob, want, atol=2e-2, rtol=1e-2)
+    K.gemm_tc2(x, w, ob, K.EPI_RELU2_BF16, n_tok, bias=bias)
+    close(ob, (want + bias.double()).clamp(min=0.0) ** 2, atol=4e-2, rtol=1e-2)
     os_ = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
     K.gemm_tc2(x, w, os_, K.EPI_SWIGLU_BF16, n_tok, w_up=wu)
     close(os_, P.silu(want) * (x.double() @ wu.double().t()), atol=2e-2, rtol=1e-2)
