@@ -40,7 +40,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 typedef __nv_bfloat16 bf16;
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -342,16 +342,22 @@ __global__ void __launch_bounds__(THREADS, 2) mixed_heads_tile_kernel(
                 split_pair(s1[2 * kk].x, s1[2 * kk].y, hi[1], lo[1]);
                 split_pair(s0[2 * kk + 1].x, s0[2 * kk + 1].y, hi[2], lo[2]);
                 split_pair(s1[2 * kk + 1].x, s1[2 * kk + 1].y, hi[3], lo[3]);
+                // four tiles of the value's size at a time, the rounded weights first and the rest after: two products into
+                // one accumulator are four instructions apart
 #pragma unroll
-                for (int v = 0; v < VT_MAX; v += 2) {
+                for (int v = 0; v < VT_MAX; v += 4) {
                     if (v < VT) {
+                        uint32_t b2[4];
                         ldsm_x4_trans(b, v_lane + (size_t)kk * 16 * VR + v * 8);
+                        if (v + 2 < VT) ldsm_x4_trans(b2, v_lane + (size_t)kk * 16 * VR + (v + 2) * 8);
                         mma_bf16(o[v], hi, b[0], b[1]);
+                        if (v + 1 < VT) mma_bf16(o[v + 1], hi, b[2], b[3]);
+                        if (v + 2 < VT) mma_bf16(o[v + 2], hi, b2[0], b2[1]);
+                        if (v + 3 < VT) mma_bf16(o[v + 3], hi, b2[2], b2[3]);
                         mma_bf16(o[v], lo, b[0], b[1]);
-                        if (v + 1 < VT) {
-                            mma_bf16(o[v + 1], hi, b[2], b[3]);
-                            mma_bf16(o[v + 1], lo, b[2], b[3]);
-                        }
+                        if (v + 1 < VT) mma_bf16(o[v + 1], lo, b[2], b[3]);
+                        if (v + 2 < VT) mma_bf16(o[v + 2], lo, b2[0], b2[1]);
+                        if (v + 3 < VT) mma_bf16(o[v + 3], lo, b2[2], b2[3]);
                     }
                 }
             }
