@@ -17,8 +17,9 @@
 // whatever C is, so the result does not depend on the cluster's size.  The cluster barrier is the
 // hardware's (barrier.cluster): no block spins on memory.
 //
-// The sink has no key and no value, is neither scaled nor multiplied by temp, and counts once: the
-// running maximum starts at sink_h and the running sum at 1.
+// The sink is one more term e^(sink_h) of the divisor alone: sink_h is used as stored (scale and temp are for
+// products of queries and keys), and nothing is added to the numerator.  So the running maximum starts at
+// sink_h and the running sum at 1.
 #include "common.cuh"
 
 #include <cooperative_groups.h>

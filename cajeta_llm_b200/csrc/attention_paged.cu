@@ -123,8 +123,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
 //   raw_g,j   = (q_g . k_j) * scale * temp[g]                       (temp: a number per head, or none)
 //   s_h,j     = sum_g talk[h, g] raw_g,j                            (talk: [heads, heads], or none = identity)
 //   o_h       = sum_j e^(s_h,j - m) v_j / (sum_j e^(s_h,j - m) + e^(sink_h - m))   (sink: per head, or none)
-// over the keys j in [from, p] of the row's window.  The sink has no key and no value, is neither scaled
-// nor multiplied by temp, and counts once in the divisor.  The keys are walked in chunks of 32 from `from`
+// over the keys j in [from, p] of the row's window.  The sink is one more term e^(sink_h) of the
+// divisor alone: sink_h is used as stored, nothing is added to the numerator.  The keys are walked in chunks of 32 from `from`
 // on, the cut depending on the row's own range only: a warp takes heads in turn (lane = key) for the raw
 // scores, the block meets, then a warp mixes and sums for its heads with a running maximum that starts at
 // the sink.  All arithmetic is float32.

@@ -21,7 +21,7 @@ sublayers the layer's ``stream_after`` part, when it has one, runs on the stream
 ``sandwich``: a norm before AND after each sublayer: ``hs += norm_1b(mixer(c(norm_1(hs))))``,
 ``hs += norm_2b(feed_forward(norm_2(hs)))``; a layer may have no feed-forward.  ``c`` is an optional causal
 convolution over time on the mixer's input (``input_conv``: ``{"taps": n, "name": tensor}``):
-``c(h)_t = h_t + sum_j w[:, j] h_(t - taps + 1 + j)`` per channel, zeros before the sequence's start, weights
+``c(h)_t = h_t + sum_j w[:, j] h_(t - taps + 1 + j)`` per channel, rows before a request's first token read as zeros, weights
 ``[hidden, taps]``; it runs in float32 on the float32 normed row, and the last ``taps - 1`` normed rows of a
 request are per-request state.  The block therefore declares state itself (``state_need()``): the
 convolution's share first, then the mixer's, which the mixer finds at ``entry.state_offset``.  Parameters:

@@ -209,7 +209,7 @@ def test_attention_sink_window_and_mixed_heads_by_hand():
     q2 = np.array([1.0, 1.0])
     raw0 = np.array([k[1] @ q2, k[2] @ q2])
     s0, s1 = raw0, 0.5 * raw0 + 0.5 * 2.0 * raw0
-    w0 = np.exp(s0) / (np.exp(s0).sum() + 1.0)                       # the sink counts once, with e^0
+    w0 = np.exp(s0) / (np.exp(s0).sum() + 1.0)                       # the divisor's extra term: e^sink with sink = 0
     w1 = np.exp(s1) / np.exp(s1).sum()                               # no sink for head 1
     want = w0 @ h[1:3] + w1 @ h[1:3]
     assert np.allclose(out[2], want)
