@@ -192,6 +192,11 @@ def run(args, peaks) -> int:
                 r.release(sl)
 
             def classes(entries_of, rows, ctx, prefill):
+                # one launch after the other on one stream: a mixer that runs its halves on two streams is told not to,
+                # so that the time between two events belongs to the launch between them
+                for blk in r.model.blocks:
+                    if hasattr(getattr(blk, "mixer", None), "overlap"):
+                        blk.mixer.overlap = False
                 spent = {}
                 for keep in (False, False, True):
                     held, entries = entries_of()

@@ -7,7 +7,8 @@ Parameters: ``hidden_size``, ``eps``, ``coef`` (default 0.5), ``left`` / ``right
 ``left_name`` / ``right_name`` (their tensor-name prefixes under this part's), ``left_out`` / ``right_out`` (the
 tensor names of the two weights).  At most one of the two may cache keys and values (the entry's cache plane is
 that one's); both may keep per-request state: the entry's state vector holds the left one's share first, then the
-right one's, and each finds its own at ``entry.state_offset``.
+right one's, and each finds its own at ``entry.state_offset``.  ``overlap`` (default true): on a CUDA device the left
+mixer runs on a side stream while the right one runs on the step's.
 """
 from __future__ import annotations
 
@@ -42,6 +43,9 @@ class SideBySide(Part):
         need = self.left.state_need()
         self.left_state = int(need.shape[0]) if need is not None else 0
         self.w_left = self.w_right = None
+        # ``overlap`` (default true): the two mixers run on two streams
+        self.overlap = bool(spec.get("overlap", True))
+        self._side = None
 
     def cache_need(self):
         return self.left.cache_need() or self.right.cache_need()
@@ -76,8 +80,25 @@ class SideBySide(Part):
         base = getattr(entry, "state_offset", 0)
         a = torch.zeros(residual.shape, dtype=torch.float32, device=residual.device)
         b = torch.zeros(residual.shape, dtype=torch.float32, device=residual.device)
-        self.left.forward(x, a, ctx, replace(entry, state_offset=base))
-        self.right.forward(x, b, ctx, replace(entry, state_offset=base + self.left_state))
+        left_entry = replace(entry, state_offset=base)
+        right_entry = replace(entry, state_offset=base + self.left_state)
+        if self.overlap and residual.is_cuda:
+            # the two halves share nothing but their input: the left one runs on a stream of its own beside the right
+            # one (their shares of the state vector and the cache planes are apart), and both are back before the
+            # norms read them.  What the left half allocates is its stream's and is freed to it; x, a and b are the
+            # step's stream's, which waits for the side stream before anything of them is given back.  A step that
+            # is being captured records the fork and the join as the graph's branches.
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=residual.device)
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                self.left.forward(x, a, ctx, left_entry)
+            self.right.forward(x, b, ctx, right_entry)
+            main.wait_stream(self._side)
+        else:
+            self.left.forward(x, a, ctx, left_entry)
+            self.right.forward(x, b, ctx, right_entry)
         K.tag = "norm + mix"
         K.rmsnorm_mix2(a, self.w_left, b, self.w_right, self.eps, self.coef, residual, accumulate=True)
         K.tag = None
