@@ -384,6 +384,28 @@ def test_captured_steps_equal_uncaptured_ones(folders):
     assert torch.equal(outs[0], outs[1])
 
 
+def test_two_streams_equal_one(folders):
+    """The halves of a parallel layer on two streams give the bits they give one after the other, in steps launched
+    kernel by kernel and in captured ones."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    d, (cfg, W) = folders("wide", CONFIGS["wide"], seed=7)
+    toks = [helpers.random_tokens(cfg["vocab"], 80, seed=90 + i) for i in range(2)]
+    outs = []
+    for overlap in (True, False):
+        r = runner_for(d, "bfloat16", max_tokens=128, cuda_graphs=True)
+        pairs = [b.mixer for b in r.model.blocks if hasattr(b.mixer, "overlap")]
+        assert pairs and all(m.overlap for m in pairs)
+        for m in pairs:
+            m.overlap = overlap
+        slots = [r.admit() for _ in toks]
+        got = [r.step([StepEntry(s, t[:37], [36]) for s, t in zip(slots, toks)]).cpu()]
+        for i in range(37, 80):
+            got.append(r.step([StepEntry(s, [t[i]], [0]) for s, t in zip(slots, toks)]).cpu())
+        outs.append(torch.cat(got))
+        assert r.graph_replays > 0
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_a_folder_whose_configuration_leaves_the_decay_rank_to_the_tensor(folders, tmp_path):
     """The decay's inner size is the shape of a tensor: a folder's config.json need not give it."""
     import shutil
