@@ -5,6 +5,6 @@ entry points are :class:`cajeta_llm_b200.engine.llm_engine.LlmEngine` (load, sub
 generate), ``python -m cajeta_llm_b200`` (command line) and ``bin/trace_run``.
 """
 from . import parts  # noqa: F401  (registers the built-in parts)
-from .models import balalorn, govuvik, qwen2_moe, saropel  # noqa: F401  (register the architectures)
+from .models import balalorn, dimuvik, govuvik, qwen2_moe, saropel  # noqa: F401  (register the architectures)
 
 __version__ = "0.1.0"

@@ -290,6 +290,8 @@ CJ_EXPORT int cj_paged_attention(const void* q, void* out, int act_dtype, const 
 // cos and sin multiplied by `magnitude`; queries go to q_out, keys and values to the row's
 // place in the paged cache.  v_off < 0: the values are the keys as projected, before norm
 // and rotation (vd == hd then).  All arithmetic is float32.
+// `q_temp_coef` != 0: the queries (not the keys) are multiplied by 1 + coef ln(floor((p + 1) / every) + 1), a temperature
+// that grows with the row's position p in steps of `every` tokens.
 // `whole`: the norm's statistic is taken over all heads of q (of k) at once, mean over n_heads * hd
 // (n_kv * hd) entries, and the weight has that many entries, a head reading its own stretch.
 // ---------------------------------------------------------------------------------
@@ -312,7 +314,8 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(
     const float* __restrict__ x, int ld, int q_off, int k_off, int v_off, TQ* __restrict__ q_out, TC* __restrict__ kplane,
     TC* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req, const int* __restrict__ table,
     int table_stride, int page_tokens, int T, int n_heads, int n_kv, int hd, int vd, int rot, const float* __restrict__ inv_freq,
-    float magnitude, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, int write_kv, int whole) {
+    float magnitude, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, int write_kv, int whole,
+    float q_temp_coef, int q_temp_every) {
     cj::after_predecessor();
     cj::release_successor();
     extern __shared__ __align__(16) float cs[];      // cos[half] then sin[half], times the magnitude
@@ -321,6 +324,8 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = rot >> 1;
+    // a query's temperature grows with its position in steps of `every` tokens: 1 + coef ln(floor((p + 1) / every) + 1)
+    const float q_temp = q_temp_coef != 0.0f ? 1.0f + q_temp_coef * logf((float)((pos + 1) / q_temp_every) + 1.0f) : 1.0f;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         const float ang = (float)pos * inv_freq[i];
         cs[i] = cosf(ang) * magnitude;
@@ -389,6 +394,7 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(
             ss = warp_sum(ss);
             inv = 1.0f / sqrtf(ss / (float)hd + eps);
         }
+        if (is_q) inv *= q_temp;
         if (vec) {
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
@@ -437,13 +443,14 @@ CJ_EXPORT int cj_head_prepare(const float* x, int ld, int q_off, int k_off, int 
                               void* vplane, int cache_dtype, const int* positions, const int* row_req, const int* table,
                               int table_stride, int page_tokens, int T, int n_heads, int n_kv, int hd, int vd, int rotary_dim,
                               const float* inv_freq, float magnitude, const float* q_norm, const float* k_norm, float eps,
-                              int write_kv, int whole, cudaStream_t stream) {
+                              int write_kv, int whole, float q_temp_coef, int q_temp_every, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!x || !q_out || !positions || n_heads <= 0 || hd <= 0 || vd <= 0) return CJ_ERR_ARG;
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return CJ_ERR_SIZE;
     if (rotary_dim > 0 && !inv_freq) return CJ_ERR_ARG;
     if (write_kv && (!kplane || !vplane || !row_req || !table || page_tokens <= 0 || n_kv <= 0)) return CJ_ERR_ARG;
     if (v_off < 0 && vd != hd) return CJ_ERR_SIZE;
+    if (q_temp_coef != 0.0f && q_temp_every < 1) return CJ_ERR_SIZE;
     // a warp a head; with few rows the heads of a row go over several blocks
     const int slots = n_heads + (write_kv ? n_kv : 0);
     int parts = T >= 128 ? 1 : (slots + 3) / 4;
@@ -453,7 +460,7 @@ CJ_EXPORT int cj_head_prepare(const float* x, int ld, int q_off, int k_off, int 
 #define LAUNCH(TQ, TC)                                                                                                  \
     cj::launch(head_prepare_kernel<TQ, TC>, dim3(grid), dim3(128), smem, stream, x, ld, q_off, k_off, v_off, (TQ*)q_out,  \
         (TC*)kplane, (TC*)vplane, positions, row_req, table, table_stride, page_tokens, T, n_heads, n_kv, hd, vd,      \
-        rotary_dim, inv_freq, magnitude, q_norm, k_norm, eps, write_kv, whole)
+        rotary_dim, inv_freq, magnitude, q_norm, k_norm, eps, write_kv, whole, q_temp_coef, q_temp_every)
     if (q_dtype == CJ_F32 && cache_dtype == CJ_F32) LAUNCH(float, float);
     else if (q_dtype == CJ_BF16 && cache_dtype == CJ_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else return CJ_ERR_DTYPE;

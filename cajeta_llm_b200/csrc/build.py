@@ -35,6 +35,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_simt": "gemm_simt.cu",
     "attention_paged": "attention_paged.cu",
     "attention_mixed": "attention_mixed.cu",
+    "attention_diff": "attention_diff.cu",
     "moe_route": "moe_route.cu",
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",

@@ -160,6 +160,44 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     _check(st, "rmsnorm")
 
 
+def dyt(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, alpha: float, out: torch.Tensor,
+        out_f32: Optional[torch.Tensor] = None, row_index: Optional[torch.Tensor] = None,
+        partials: Optional[torch.Tensor] = None, out_split: Optional[torch.Tensor] = None) -> None:
+    """out[r] = tanh(alpha x[row_index[r] or r]) * weight + bias: the norm without statistics.  x, weight, bias float32;
+    out float32 or bfloat16; ``out_f32``, ``partials`` and ``out_split`` as for :func:`rmsnorm`."""
+    _need(x, "x", torch.float32), _need(weight, "weight", torch.float32), _need(bias, "bias", torch.float32), _need(out, "out")
+    rows, H = out.shape
+    if x.shape[-1] != H or weight.numel() != H or bias.numel() != H:
+        raise KernelError(f"dyt: width mismatch x {tuple(x.shape)} weight {tuple(weight.shape)} bias {tuple(bias.shape)} out {tuple(out.shape)}")
+    if out_f32 is not None:
+        _need(out_f32, "out_f32", torch.float32)
+    if row_index is not None:
+        _need(row_index, "row_index", torch.int32)
+    if out_split is not None:
+        _need(out_split, "out_split", torch.bfloat16)
+        if tuple(out_split.shape) != (rows, 3 * H):
+            raise KernelError(f"dyt: out_split {tuple(out_split.shape)} is not [{rows}, {3 * H}]")
+    n_part, part_stride = 0, 0
+    if partials is not None:
+        _need(partials, "partials", torch.float32)
+        if partials.dim() != 3 or partials.shape[1] != rows or partials.shape[2] != H or row_index is not None:
+            raise KernelError(f"dyt: partials {tuple(partials.shape)} do not fit {rows} rows of {H}")
+        n_part, part_stride = partials.shape[0], partials.stride(0)
+    st = library("rowwise").cj_dyt(_ptr(x), _ptr(weight), _ptr(bias), _f(alpha), _i(rows), _i(H), _ptr(out), _i(_code(out)),
+                                   _ptr(out_f32), _ptr(out_split), _ptr(row_index), _ptr(partials), _i(n_part), _ll(part_stride),
+                                   _stream())
+    _check(st, "dyt")
+
+
+def dyt_add(hs: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, alpha: float) -> None:
+    """hs[r] += tanh(alpha y[r]) * weight + bias; everything float32."""
+    _need(hs, "hs", torch.float32), _need(y, "y", torch.float32), _need(weight, "weight", torch.float32), _need(bias, "bias", torch.float32)
+    rows, H = hs.shape
+    if y.shape != hs.shape or weight.numel() != H or bias.numel() != H:
+        raise KernelError(f"dyt_add: shapes hs {tuple(hs.shape)} y {tuple(y.shape)} weight {tuple(weight.shape)} do not agree")
+    _check(library("rowwise").cj_dyt_add(_ptr(hs), _ptr(y), _ptr(weight), _ptr(bias), _f(alpha), _i(rows), _i(H), _stream()), "dyt_add")
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
          accumulate: bool = False, w_up: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
          a_row_index: Optional[torch.Tensor] = None, rows: Optional[int] = None, act_limit: float = 0.0,
@@ -224,13 +262,15 @@ def head_prepare(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: tor
                  v_plane: Optional[torch.Tensor], positions: torch.Tensor, row_req: Optional[torch.Tensor],
                  table: Optional[torch.Tensor], page_tokens: int, n_heads: int, n_kv: int, head_dim: int, value_dim: int,
                  rotary_dim: int, inv_freq: Optional[torch.Tensor], magnitude: float, q_norm: Optional[torch.Tensor],
-                 k_norm: Optional[torch.Tensor], eps: float, write_kv: bool, norm_whole: bool = False) -> None:
+                 k_norm: Optional[torch.Tensor], eps: float, write_kv: bool, norm_whole: bool = False,
+                 q_temp_coef: float = 0.0, q_temp_every: int = 1) -> None:
     """Queries, keys and values of a step's rows (x float32 [T, ld], columns from q_off, k_off, v_off) made ready
     for attention: an RMS norm over each head of q and k (when ``q_norm`` / ``k_norm``, float32 [head_dim], are
     given), the rotation of their first ``rotary_dim`` entries (entry i with i + rotary_dim / 2; cos and sin times
     ``magnitude``), q to ``q_out``, k and v into the cache pages of the row's request.  ``v_off`` < 0: the
     values are the keys as projected, before norm and rotation.  ``norm_whole``: one statistic over all heads of q
-    (of k) at once, and weights of ``n_heads * head_dim`` (``n_kv * head_dim``) entries."""
+    (of k) at once, and weights of ``n_heads * head_dim`` (``n_kv * head_dim``) entries.  ``q_temp_coef`` != 0: the
+    queries are multiplied by ``1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1)`` at position p."""
     _need(x, "x", torch.float32), _need(q_out, "q_out"), _need(positions, "positions", torch.int32)
     cache_dtype = _code(q_out)
     if write_kv:
@@ -247,7 +287,8 @@ def head_prepare(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: tor
         _ptr(x), _i(x.stride(0)), _i(q_off), _i(k_off), _i(v_off), _ptr(q_out), _i(_code(q_out)), _ptr(k_plane), _ptr(v_plane),
         _i(cache_dtype), _ptr(positions), _ptr(row_req), _ptr(table), _i(table.stride(0) if table is not None else 0),
         _i(page_tokens), _i(x.shape[0]), _i(n_heads), _i(n_kv), _i(head_dim), _i(value_dim), _i(rotary_dim), _ptr(inv_freq),
-        _f(magnitude), _ptr(q_norm), _ptr(k_norm), _f(eps), _i(1 if write_kv else 0), _i(1 if norm_whole else 0), _stream())
+        _f(magnitude), _ptr(q_norm), _ptr(k_norm), _f(eps), _i(1 if write_kv else 0), _i(1 if norm_whole else 0),
+        _f(q_temp_coef), _i(q_temp_every), _stream())
     _check(st, "head_prepare")
 
 
@@ -277,6 +318,27 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v
         _ptr(row_req), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim),
         _i(value_dim or head_dim), _i(window), _f(scale), _f(softcap), gate_ptr, _i(gate_ld), _stream())
     _check(st, "paged_attention")
+
+
+def diff_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, positions: torch.Tensor,
+                   row_req: torch.Tensor, table: torch.Tensor, page_tokens: int, n_heads: int, n_kv: int, head_dim: int,
+                   value_dim: int, window: int, scale: float, lam: float, eps: float, out_scale: float) -> None:
+    """Differential attention of every row over its request's cached keys [from, position]: a query head is
+    [q1 | q2] (``head_dim`` entries each), a cached key [k1 | k2]; each map is a softmax attention of its own over the
+    same values, ``o = a1 - lam a2``, then ``o / sqrt(mean(o^2) + eps) * out_scale`` over the head's ``value_dim`` entries.
+    q [T, n_heads, 2 head_dim], out [T, n_heads, value_dim]."""
+    _need(q, "q"), _need(out, "out", q.dtype), _need(k_plane, "k_plane"), _need(v_plane, "v_plane", k_plane.dtype)
+    _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
+    T = q.shape[0]
+    if q.numel() != T * n_heads * 2 * head_dim or out.numel() != T * n_heads * value_dim:
+        raise KernelError("diff_attention: q or out does not have the heads' sizes")
+    if k_plane.shape[-1] != 2 * head_dim or v_plane.shape[-1] != value_dim:
+        raise KernelError("diff_attention: the cache planes do not have the heads' sizes")
+    st = library("attention_diff").cj_diff_attention(
+        _ptr(q), _ptr(out), _i(_code(q)), _ptr(k_plane), _ptr(v_plane), _i(_code(k_plane)), _ptr(positions), _ptr(row_req),
+        _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim), _i(value_dim), _i(window),
+        _f(scale), _f(lam), _f(eps), _f(out_scale), _stream())
+    _check(st, "diff_attention")
 
 
 _sms: Dict[int, int] = {}
@@ -375,17 +437,29 @@ def _pin_and_gap(pin: Optional[torch.Tensor], gap: Optional[torch.Tensor], T: in
             raise KernelError(f"router: gap must hold {T} margins")
 
 
+def _correction(correction: Optional[torch.Tensor], num_experts: int, groups) -> None:
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+        if correction.numel() != num_experts:
+            raise KernelError(f"router: correction must hold {num_experts} entries, found {correction.numel()}")
+        if groups is not None and int(groups[0]) > 1:
+            raise KernelError("router: a choice correction together with expert groups is not built")
+
+
 def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[torch.Tensor], top_k: int,
                 norm_topk: bool, sel: torch.Tensor, weights: torch.Tensor, shared_scale: Optional[torch.Tensor],
                 pin: Optional[torch.Tensor] = None, gap: Optional[torch.Tensor] = None, sigmoid_scores: bool = False,
-                groups=None) -> None:
+                groups=None, correction: Optional[torch.Tensor] = None, weight_scale: float = 1.0) -> None:
     """Router logits, softmax over all experts (or, with ``sigmoid_scores``, each expert's own
     sigmoid), top-k and the shared expert's sigmoid gate.
     ``pin`` (int32 [T, k]): the experts are given, not chosen; the weights are still the row's own
     probabilities of them.  ``gap`` (float32 [T], not with ``pin``): each row's routing margin
     (p_k - p_{k+1}) / p_k out.  ``groups`` = (count, keep): the experts form ``count`` equal groups of
-    neighbours and only those of the ``keep`` groups with the largest best score can be picked."""
+    neighbours and only those of the ``keep`` groups with the largest best score can be picked.
+    ``correction`` (float32 [E]): added to the scores for the choice alone, a pick's weight stays its score;
+    ``weight_scale`` multiplies the picks' weights."""
     _need(x, "x", torch.float32), _need(router_w, "router_w", torch.float32)
+    _correction(correction, router_w.shape[0], groups)
     _need(sel, "sel", torch.int32), _need(weights, "weights", torch.float32)
     T, H = x.shape
     E = router_w.shape[0]
@@ -402,7 +476,8 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
         tickets = _router_tickets[x.device] = torch.zeros((4,), dtype=torch.int32, device=x.device)
     st = library("moe_route").cj_router_topk(_ptr(x), _ptr(router_w), _ptr(shared_gate), _i(T), _i(H), _i(E), _i(top_k),
                                              _i(_route_mode(norm_topk, sigmoid_scores, groups)), _ptr(sel), _ptr(weights),
-                                             _ptr(shared_scale), _ptr(logits), _ptr(tickets), _ptr(pin), _ptr(gap), _stream())
+                                             _ptr(shared_scale), _ptr(logits), _ptr(tickets), _ptr(pin), _ptr(gap),
+                                             _ptr(correction), _f(weight_scale), _stream())
     _check(st, "router_topk")
     if T > 32:
         global launches
@@ -411,7 +486,8 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
 
 def router_select(partials: torch.Tensor, num_experts: int, top_k: int, norm_topk: bool, sel: torch.Tensor,
                   weights: torch.Tensor, shared_scale: Optional[torch.Tensor], pin: Optional[torch.Tensor] = None,
-                  gap: Optional[torch.Tensor] = None, sigmoid_scores: bool = False, groups=None) -> None:
+                  gap: Optional[torch.Tensor] = None, sigmoid_scores: bool = False, groups=None,
+                  correction: Optional[torch.Tensor] = None, weight_scale: float = 1.0) -> None:
     """Softmax over all experts, top-k and the shared gate's sigmoid from router logits given
     as partial sums ``[S, T, ld]`` (float32; column ``num_experts`` holds the gate's dot when
     ``shared_scale`` is given); the partials of a row are added in order first."""
@@ -422,11 +498,13 @@ def router_select(partials: torch.Tensor, num_experts: int, top_k: int, norm_top
         raise KernelError(f"router_select: {num_experts} experts; this kernel takes at most 1024")
     S, T, ld = partials.shape
     _pin_and_gap(pin, gap, T, top_k)
+    _correction(correction, num_experts, groups)
     if shared_scale is not None:
         _need(shared_scale, "shared_scale", torch.float32)
     st = library("moe_route").cj_router_select(_ptr(partials), _i(S), _ll(partials.stride(0)), _i(ld), _i(T), _i(num_experts),
                                                _i(top_k), _i(_route_mode(norm_topk, sigmoid_scores, groups)), _ptr(sel),
-                                               _ptr(weights), _ptr(shared_scale), _ptr(pin), _ptr(gap), _stream())
+                                               _ptr(weights), _ptr(shared_scale), _ptr(pin), _ptr(gap), _ptr(correction),
+                                               _f(weight_scale), _stream())
     _check(st, "router_select")
 
 
@@ -746,11 +824,16 @@ LATENT_FILL_BLOCKS = 592         # blocks that fill the machine (four an SM); fe
 
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, plane: torch.Tensor, rank: int, rot: int, heads: int,
                      positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int, scale: float,
-                     out: torch.Tensor, max_context: int = 0) -> None:
+                     out: torch.Tensor, max_context: int = 0, sink: Optional[torch.Tensor] = None) -> None:
     """Every (row, head): softmax over the row's keys [0, position] of (q_abs . c + q_rot . r) * scale,
     and the weighted sum of the latents.  q_abs float32 [heads, T, rank]; q_rot float32 [T, heads, rot];
     out [heads, T, rank] in the cache's dtype.  ``max_context`` (the longest row's keys, when the
-    caller knows it): with few rows the keys of a row are cut into stretches that run side by side."""
+    caller knows it): with few rows the keys of a row are cut into stretches that run side by side.
+    ``sink`` (float32 [heads]): the softmax's divisor also holds exp(sink[h])."""
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
+        if sink.numel() != heads:
+            raise KernelError(f"latent_attention: sink must hold {heads} entries")
     _need(q_abs, "q_abs", torch.float32), _need(q_rot, "q_rot", torch.float32), _need(plane, "plane"), _need(out, "out", plane.dtype)
     _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
     T = positions.numel()
@@ -770,7 +853,7 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, plane: torch.Tens
     st = library("latent_attention").cj_latent_attention(_ptr(q_abs), _ptr(q_rot), _ptr(plane), _i(_code(plane)), _i(rank), _i(rot),
                                                          _i(heads), _i(T), _ptr(positions), _ptr(row_req), _ptr(table),
                                                          _i(table.stride(0)), _i(page_tokens), _f(scale), _ptr(out),
-                                                         _i(split_keys), _i(splits), _ptr(part_acc), _ptr(part_ml), _stream())
+                                                         _i(split_keys), _i(splits), _ptr(part_acc), _ptr(part_ml), _ptr(sink), _stream())
     _check(st, "latent_attention")
     if split_keys:
         global launches
@@ -814,35 +897,53 @@ def latent_q_pack(q: torch.Tensor, heads: int, dim: int, rot: int, rotary: int, 
 
 
 def latent_flash(qx: torch.Tensor, out: torch.Tensor, kx: torch.Tensor, vx: torch.Tensor, req_start: torch.Tensor,
-                 req_prior: torch.Tensor, req_base: torch.Tensor, requests: int, heads: int, scale: float) -> None:
+                 req_prior: torch.Tensor, req_base: torch.Tensor, requests: int, heads: int, scale: float,
+                 sink: Optional[torch.Tensor] = None) -> None:
     """Causal attention of the step's rows (request i: rows [req_start[i], req_start[i+1]) at positions
     req_prior[i] + j) over the dense keys and values of their requests (request i's token p at
-    req_base[i] + p).  qx [T, heads, DK], kx [N, heads, DK], vx [N, heads, DV], out [T, heads, DV], bfloat16."""
+    req_base[i] + p).  qx [T, heads, DK], kx [N, heads, DK], vx [N, heads, DV], out [T, heads, DV], bfloat16.
+    ``sink`` (float32 [heads]): the softmax's divisor also holds exp(sink[h])."""
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
     for n, t in (("qx", qx), ("out", out), ("kx", kx), ("vx", vx)):
         _need(t, n, torch.bfloat16)
     for n, t in (("req_start", req_start), ("req_prior", req_prior), ("req_base", req_base)):
         _need(t, n, torch.int32)
     st = library("latent_prefill").cj_latent_flash(_ptr(qx), _ptr(out), _ptr(kx), _ptr(vx), _ptr(req_start), _ptr(req_prior), _ptr(req_base),
                                                    _i(requests), _i(qx.shape[0]), _i(heads), _i(qx.shape[2]), _i(vx.shape[2]), _f(scale),
-                                                   _stream())
+                                                   _ptr(sink), _stream())
     _check(st, "latent_flash")
 
 
-def latent_gate_rows(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, heads: int, vdim: int, out: torch.Tensor) -> None:
-    """out[t, h * vdim + e] = o[t, h, e] * sigmoid(gate[t, gate_offset + h]); o bfloat16 [T, heads, DV], gate float32."""
-    _need(o, "o", torch.bfloat16), _need(gate, "gate", torch.float32), _need(out, "out", torch.bfloat16)
-    st = library("latent_prefill").cj_latent_gate_rows(_ptr(o), _i(o.shape[2]), ctypes.c_void_p(gate.data_ptr() + 4 * gate_offset),
-                                                       _i(gate.stride(0)), _i(heads), _i(vdim), _ptr(out), _i(o.shape[0]), _stream())
+def latent_gate_rows(o: torch.Tensor, gate: Optional[torch.Tensor], gate_offset: int, heads: int, vdim: int, out: torch.Tensor) -> None:
+    """out[t, h * vdim + e] = o[t, h, e] * sigmoid(gate[t, gate_offset + h]); o bfloat16 [T, heads, DV], gate float32
+    (None: no gate, the heads' entries are only moved out of their padding)."""
+    _need(o, "o", torch.bfloat16), _need(out, "out", torch.bfloat16)
+    gate_ptr, gate_ld = _gate(gate, gate_offset)
+    st = library("latent_prefill").cj_latent_gate_rows(_ptr(o), _i(o.shape[2]), gate_ptr,
+                                                       _i(gate_ld), _i(heads), _i(vdim), _ptr(out), _i(o.shape[0]), _stream())
     _check(st, "latent_gate_rows")
 
 
-def latent_gate_out(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, heads: int, vdim: int, out: torch.Tensor) -> None:
-    """out[t, h, :] = o[h, t, :] * sigmoid(gate[t, gate_offset + h]); o float32 [heads, T, vdim], gate float32."""
-    _need(o, "o", torch.float32), _need(gate, "gate", torch.float32), _need(out, "out")
+def latent_q_norm(x: torch.Tensor, offset: int, n: int, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out[t] = rms(x[t, offset : offset + n]) * weight: the norm of a stretch of columns of a float32 matrix, into
+    ``out`` [T, n] in its own dtype."""
+    _need(x, "x", torch.float32), _need(weight, "weight", torch.float32), _need(out, "out")
+    if weight.numel() != n or tuple(out.shape) != (x.shape[0], n) or offset + n > x.shape[1]:
+        raise KernelError("latent_q_norm: sizes do not agree")
+    st = library("latent_attention").cj_latent_q_norm(_ptr(x), _i(x.stride(0)), _i(offset), _i(n), _ptr(weight), _f(eps), _ptr(out),
+                                                      _i(_code(out)), _i(x.shape[0]), _stream())
+    _check(st, "latent_q_norm")
+
+
+def latent_gate_out(o: torch.Tensor, gate: Optional[torch.Tensor], gate_offset: int, heads: int, vdim: int, out: torch.Tensor) -> None:
+    """out[t, h, :] = o[h, t, :] * sigmoid(gate[t, gate_offset + h]); o float32 [heads, T, vdim], gate float32 (None: no gate)."""
+    _need(o, "o", torch.float32), _need(out, "out")
     T = out.shape[0]
     if o.numel() != heads * T * vdim or out.shape[1] != heads * vdim:
         raise KernelError("latent_gate_out: sizes do not agree")
-    st = library("latent_attention").cj_latent_gate_out(_ptr(o), ctypes.c_void_p(gate.data_ptr() + 4 * gate_offset), _i(gate.stride(0)),
+    gate_ptr, gate_ld = _gate(gate, gate_offset)
+    st = library("latent_attention").cj_latent_gate_out(_ptr(o), gate_ptr, _i(gate_ld),
                                                         _i(heads), _i(vdim), _i(T), _ptr(out), _i(_code(out)), _stream())
     _check(st, "latent_gate_out")
 

@@ -12,7 +12,11 @@
 // latent_attention  scores, softmax and the weighted sum of latents for every (row, head);
 //                   q_abs [H, T, kv_rank] in, the summed latents [H, T, kv_rank] out (both head-major;
 //                   the sums leave in the cache's dtype, as the next product's input)
-// latent_gate_out   out[t, h, :] = o[h, t, :] * sigmoid(gate[t, h])  (back to token-major)
+// latent_gate_out   out[t, h, :] = o[h, t, :] * sigmoid(gate[t, h])  (back to token-major; without a gate: the move alone)
+// latent_q_norm     the queries' own latent: rms(x[:, offset : offset + n]) * w into the activation dtype
+//
+// A sink (optional, one float32 per head): the softmax's divisor also holds exp(sink[h]), a term without key or value
+// that is neither scaled nor rotated; the running maximum of a row's first stretch starts at it and the running sum at 1.
 //
 // The rotation pairs entries (2i, 2i+1); the angle p * inv_freq[i] is float32.  Scores,
 // softmax and sums are float32 whatever the cache holds.
@@ -106,7 +110,7 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(
     const float* __restrict__ q_abs, const float* __restrict__ q_rot, const TC* __restrict__ plane, int rank, int rot,
     int heads, int T, const int* __restrict__ positions, const int* __restrict__ row_req, const int* __restrict__ table,
     int table_stride, int page_tokens, float scale, TC* __restrict__ out, int row_words, int split_keys,
-    float* __restrict__ part_acc, float* __restrict__ part_ml) {
+    float* __restrict__ part_acc, float* __restrict__ part_ml, const float* __restrict__ sink) {
     cj::after_predecessor();
     cj::release_successor();
     extern __shared__ __align__(16) unsigned char smem[];
@@ -135,6 +139,7 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
     float m = -INFINITY, l = 0.0f;
+    if (sink && has_head && key_begin == 0) { m = sink[head]; l = 1.0f; }       // the sink counts once: in the row's first stretch
     const TC* krow_base = (const TC*)ks;
     const int row_elems = row_words * (int)(4 / sizeof(TC));
     for (int k0 = key_begin; k0 < key_end; k0 += LA_KEYS) {
@@ -281,12 +286,43 @@ __global__ void latent_gate_out_kernel(const float* __restrict__ o, const float*
     const int r = blockIdx.x;
     for (int i = threadIdx.x; i < heads * vdim; i += blockDim.x) {
         const int h = i / vdim, e = i % vdim;
-        const float g = 1.0f / (1.0f + expf(-gate[(size_t)r * ld_gate + h]));
+        const float g = gate ? 1.0f / (1.0f + expf(-gate[(size_t)r * ld_gate + h])) : 1.0f;
         out[(size_t)r * heads * vdim + i] = from_f32<TO>(o[((size_t)h * T + r) * vdim + e] * g);
     }
 }
 
+template <typename TO>
+__global__ void latent_q_norm_kernel(const float* __restrict__ x, int ld, int offset, int n, const float* __restrict__ w, float eps,
+                                     TO* __restrict__ out) {
+    cj::after_predecessor();
+    cj::release_successor();
+    __shared__ float scratch[32];
+    const float* src = x + (size_t)blockIdx.x * ld + offset;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    ss = warp_sum(ss);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) scratch[warp] = ss;
+    __syncthreads();
+    float total = 0.0f;
+    for (int i = 0; i < nw; ++i) total += scratch[i];
+    const float scale = 1.0f / sqrtf(total / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) out[(size_t)blockIdx.x * n + i] = from_f32<TO>(src[i] * scale * w[i]);
+}
+
 }  // namespace
+
+// out [T, n] = rms(x[:, offset : offset + n]) * w; x float32 with row stride ld
+CJ_EXPORT int cj_latent_q_norm(const float* x, int ld, int offset, int n, const float* w, float eps, void* out, int out_dtype, int T,
+                               cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!x || !w || !out || n <= 0 || offset < 0 || ld < offset + n) return CJ_ERR_ARG;
+    const int threads = n >= 1024 ? 256 : 128;
+    if (out_dtype == CJ_F32) cj::launch(latent_q_norm_kernel<float>, dim3(T), dim3(threads), 0, stream, x, ld, offset, n, w, eps, (float*)out);
+    else if (out_dtype == CJ_BF16) cj::launch(latent_q_norm_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, x, ld, offset, n, w, eps, (__nv_bfloat16*)out);
+    else return CJ_ERR_DTYPE;
+    return launch_status();
+}
 
 CJ_EXPORT int cj_latent_kv_write(const float* d, int ld, int rank, int rot, int rotary, const float* w, float eps, const float* inv_freq,
                                  const int* positions, const int* row_req, const int* table, int table_stride, int page_tokens,
@@ -319,7 +355,7 @@ CJ_EXPORT int cj_latent_q_split(const float* q, int ld, int heads, int dim, int 
 CJ_EXPORT int cj_latent_attention(const float* q_abs, const float* q_rot, const void* plane, int cache_dtype, int rank, int rot,
                                   int heads, int T, const int* positions, const int* row_req, const int* table, int table_stride,
                                   int page_tokens, float scale, void* out, int split_keys, int splits, float* part_acc,
-                                  float* part_ml, cudaStream_t stream) {
+                                  float* part_ml, const float* sink, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!q_abs || !q_rot || !plane || !positions || !row_req || !table || !out) return CJ_ERR_ARG;
     if (rank <= 0 || rank > 1024 || rot < 0 || heads <= 0 || page_tokens <= 0) return CJ_ERR_SIZE;
@@ -344,7 +380,7 @@ CJ_EXPORT int cj_latent_attention(const float* q_abs, const float* q_rot, const 
         }                                                                                                              \
         cj::launch(latent_attention_kernel<TC, N>, grid, dim3(LA_HEADS * 32), smem, stream, q_abs, q_rot, (const TC*)plane, \
                    rank, rot, heads, T, positions, row_req, table, table_stride, page_tokens, scale, (TC*)out, row_words, \
-                   split_keys, pa, pm);                                                                                \
+                   split_keys, pa, pm, sink);                                                                          \
         if (split_keys > 0)                                                                                            \
             cj::launch(latent_merge_kernel<TC>, dim3(T, heads), dim3(128), 0, stream, (const float*)pa, (const float*)pm, splits, \
                        split_keys, rank, heads, T, positions, (TC*)out);                                               \
@@ -367,7 +403,7 @@ CJ_EXPORT int cj_latent_attention(const float* q_abs, const float* q_rot, const 
 CJ_EXPORT int cj_latent_gate_out(const float* o, const float* gate, int ld_gate, int heads, int vdim, int T, void* out,
                                  int out_dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (!o || !gate || !out || heads <= 0 || vdim <= 0) return CJ_ERR_ARG;
+    if (!o || !out || heads <= 0 || vdim <= 0) return CJ_ERR_ARG;
     int threads = heads * vdim >= 2048 ? 256 : 128;
     if (out_dtype == CJ_F32) cj::launch(latent_gate_out_kernel<float>, dim3(T), dim3(threads), 0, stream, o, gate, ld_gate, heads, vdim, T, (float*)out);
     else if (out_dtype == CJ_BF16) cj::launch(latent_gate_out_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, o, gate, ld_gate, heads, vdim, T, (__nv_bfloat16*)out);

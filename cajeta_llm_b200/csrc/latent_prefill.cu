@@ -66,7 +66,7 @@ template <int DK, int DV>
 __global__ void __launch_bounds__(THREADS) latent_flash_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kx,
     const __nv_bfloat16* __restrict__ vx, const int* __restrict__ req_start, const int* __restrict__ req_prior,
-    const int* __restrict__ req_base, int n_requests, int n_heads, float scale_log2) {
+    const int* __restrict__ req_base, int n_requests, int n_heads, float scale_log2, const float* __restrict__ sink) {
     cj::after_predecessor();
     cj::release_successor();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -220,6 +220,12 @@ __global__ void __launch_bounds__(THREADS) latent_flash_kernel(
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (sink) {
+        // one more term of the divisor, without key or value: exp(sink), in the units of the running maximum (log 2)
+        const float s2 = sink[h] * 1.4426950408889634f;
+        l0 += exp2f(s2 - mrun[0]);
+        l1 += exp2f(s2 - mrun[1]);
+    }
     const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
     const int r0 = wrow + g, r1 = r0 + 8;
 #pragma unroll
@@ -299,7 +305,7 @@ __global__ void latent_gate_rows_kernel(const __nv_bfloat16* __restrict__ o, int
     const int r = blockIdx.x;
     for (int i = threadIdx.x; i < heads * vdim; i += blockDim.x) {
         const int h = i / vdim, e = i % vdim;
-        const float g = 1.0f / (1.0f + expf(-gate[(size_t)r * ld_gate + h]));
+        const float g = gate ? 1.0f / (1.0f + expf(-gate[(size_t)r * ld_gate + h])) : 1.0f;
         out[(size_t)r * heads * vdim + i] = __float2bfloat16_rn(__bfloat162float(o[((size_t)r * heads + h) * DV + e]) * g);
     }
 }
@@ -340,7 +346,7 @@ CJ_EXPORT int cj_latent_q_pack(const float* q, int ld, int heads, int dim, int r
 // q [T, heads, DK], kx [N, heads, DK], vx [N, heads, DV], out [T, heads, DV], all bf16; DK in {64, 128, 192, 256}, DV in {64, 128}
 CJ_EXPORT int cj_latent_flash(const void* q, void* out, const void* kx, const void* vx, const int* req_start, const int* req_prior,
                               const int* req_base, int n_requests, int total_rows, int heads, int DK, int DV, float scale,
-                              cudaStream_t stream) {
+                              const float* sink, cudaStream_t stream) {
     if (total_rows <= 0 || n_requests <= 0) return 0;
     if (!q || !out || !kx || !vx || !req_start || !req_prior || !req_base) return CJ_ERR_ARG;
     if (heads <= 0 || heads > 65535) return CJ_ERR_SIZE;
@@ -356,7 +362,7 @@ CJ_EXPORT int cj_latent_flash(const void* q, void* out, const void* kx, const vo
             configured = true;                                                                                           \
         }                                                                                                                \
         cj::launch(latent_flash_kernel<K_, V_>, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, \
-                   (const __nv_bfloat16*)kx, (const __nv_bfloat16*)vx, req_start, req_prior, req_base, n_requests, heads, scale_log2); \
+                   (const __nv_bfloat16*)kx, (const __nv_bfloat16*)vx, req_start, req_prior, req_base, n_requests, heads, scale_log2, sink); \
         return launch_status();                                                                                          \
     }
     if (DV == 64) {
@@ -377,7 +383,7 @@ CJ_EXPORT int cj_latent_flash(const void* q, void* out, const void* kx, const vo
 CJ_EXPORT int cj_latent_gate_rows(const void* o, int DV, const float* gate, int ld_gate, int heads, int vdim, void* out, int T,
                                   cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (!o || !gate || !out || heads <= 0 || vdim <= 0 || DV < vdim) return CJ_ERR_ARG;
+    if (!o || !out || heads <= 0 || vdim <= 0 || DV < vdim) return CJ_ERR_ARG;
     cj::launch(latent_gate_rows_kernel, dim3(T), dim3(heads * vdim >= 2048 ? 256 : 128), 0, stream, (const __nv_bfloat16*)o, DV, gate,
                ld_gate, heads, vdim, (__nv_bfloat16*)out);
     return launch_status();

@@ -106,7 +106,8 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_logits_kernel(
 // from another choice (model/MoeFfn.cajeta:135-149).
 __device__ __forceinline__ void select_row(const float* row, int t, int E, int k, int norm_topk, int* __restrict__ sel,
                                            float* __restrict__ w, float* __restrict__ shared_scale, float* probs, int lane,
-                                           const int* __restrict__ pin, float* __restrict__ gap) {
+                                           const int* __restrict__ pin, float* __restrict__ gap,
+                                           const float* __restrict__ corr, float wscale) {
     if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-row[E]));
     // bit 1 of norm_topk: an expert's score is the sigmoid of its own logit instead of the
     // softmax over all experts (bit 0 still asks for the picked scores to be renormalised)
@@ -139,12 +140,12 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
                 int e = pin[t * k + j];
                 float p = (e >= 0 && e < E) ? probs[e] : __int_as_float(0x7fc00000);   // a pick outside the experts shows as NaN
                 sel[t * k + j] = (e >= 0 && e < E) ? e : 0;
-                w[t * k + j] = p;
+                w[t * k + j] = norm_topk ? p : p * wscale;
                 total += p;
             }
             if (norm_topk) {
                 if (total < 0.00006103515625f) total = 0.00006103515625f;
-                for (int j = 0; j < k; ++j) w[t * k + j] = w[t * k + j] / total;
+                for (int j = 0; j < k; ++j) w[t * k + j] = w[t * k + j] / total * wscale;
             }
         }
         return;
@@ -173,13 +174,19 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
             __syncwarp();
         }
     }
+    // corr (or null): a number per expert that is added to its score for the CHOICE alone; the weight of a pick stays
+    // its score.  A picked expert's score becomes -1 (scores are never negative), whatever its choice score was.
+    // wscale multiplies the weights at the end.
     float wsum = 0.0f, last = 0.0f, mine = 0.0f;
     for (int j = 0; j < k; ++j) {
         float bp = -1.0f;
         int best = -1;
         for (int e = lane; e < E; e += 32) {
             float p = probs[e];
-            if (p >= 0.0f && (best < 0 || p > bp)) { best = e; bp = p; }
+            if (p >= 0.0f) {
+                if (corr) p += corr[e];
+                if (best < 0 || p > bp) { best = e; bp = p; }
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -191,29 +198,33 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
         // every probability failed '>= 0': the logits of this row are not finite; the
         // pick falls to expert j with a NaN weight so that the fault shows in the logits
         if (best < 0) { best = j < E ? j : 0; bp = __int_as_float(0x7fc00000); }
-        else if (lane == 0) probs[best] = -1.0f;
+        else {
+            if (corr) { last = bp; bp = probs[best]; __syncwarp(); }
+            if (lane == 0) probs[best] = -1.0f;
+        }
         // a pick's weight stays with lane j until the sum is known (picks past 31 go through memory)
         const bool held = norm_topk && j < 32;
         if (held && lane == j) mine = bp;
         if (lane == 0) {
             sel[t * k + j] = best;
-            if (!held) w[t * k + j] = bp;
+            if (!held) w[t * k + j] = norm_topk ? bp : bp * wscale;
         }
         wsum += bp;
-        last = bp;
+        if (!corr) last = bp;                        // with corr: the last pick's choice score, kept above
         __syncwarp();
     }
     if (gap) {
-        float next = -1.0f;                          // the largest probability left
-        for (int e = lane; e < E; e += 32) next = fmaxf(next, probs[e]);
+        float next = -INFINITY;                      // the largest (choice) score left
+        for (int e = lane; e < E; e += 32)
+            if (probs[e] >= 0.0f) next = fmaxf(next, probs[e] + (corr ? corr[e] : 0.0f));
         next = warp_max(next);
         if (lane == 0) gap[t] = (k < E && last > 0.0f) ? (last - next) / last : 1.0f;
     }
     if (norm_topk) {
         if (wsum < 0.00006103515625f) wsum = 0.00006103515625f;
-        if (lane < k) w[t * k + lane] = mine / wsum;
+        if (lane < k) w[t * k + lane] = mine / wsum * wscale;
         if (lane == 0)
-            for (int j = 32; j < k; ++j) w[t * k + j] = w[t * k + j] / wsum;
+            for (int j = 32; j < k; ++j) w[t * k + j] = w[t * k + j] / wsum * wscale;
     }
 }
 
@@ -228,7 +239,8 @@ constexpr int SMALL_ROWS = 8;
 __global__ void __launch_bounds__(SMALL_ROWS * 32) router_small_kernel(
     const float* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ shared_gate, int T, int H,
     int E, int k, int norm_topk, float* __restrict__ logits, int* __restrict__ sel, float* __restrict__ w,
-    float* __restrict__ shared_scale, int* __restrict__ tickets, const int* __restrict__ pin, float* __restrict__ gap) {
+    float* __restrict__ shared_scale, int* __restrict__ tickets, const int* __restrict__ pin, float* __restrict__ gap,
+    const float* __restrict__ corr, float wscale) {
     cj::release_successor();
     __shared__ float probs[SMALL_ROWS][MAX_EXPERTS];
     __shared__ int is_last;
@@ -294,17 +306,18 @@ __global__ void __launch_bounds__(SMALL_ROWS * 32) router_small_kernel(
     if (!is_last) return;
     __threadfence();
     if (t < T) {
-        select_row(logits + (size_t)t * n_cols, t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane, pin, gap);
+        select_row(logits + (size_t)t * n_cols, t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane, pin, gap, corr, wscale);
     }
 }
 
 __global__ void __launch_bounds__(32) router_select_kernel(
     const float* __restrict__ logits, int E, int n_cols, int k, int norm_topk, int* __restrict__ sel,
-    float* __restrict__ w, float* __restrict__ shared_scale, const int* __restrict__ pin, float* __restrict__ gap) {
+    float* __restrict__ w, float* __restrict__ shared_scale, const int* __restrict__ pin, float* __restrict__ gap,
+    const float* __restrict__ corr, float wscale) {
     cj::after_predecessor();
     cj::release_successor();
     __shared__ float probs[MAX_EXPERTS];
-    select_row(logits + (size_t)blockIdx.x * n_cols, blockIdx.x, E, k, norm_topk, sel, w, shared_scale, probs, threadIdx.x, pin, gap);
+    select_row(logits + (size_t)blockIdx.x * n_cols, blockIdx.x, E, k, norm_topk, sel, w, shared_scale, probs, threadIdx.x, pin, gap, corr, wscale);
 }
 
 // The selection from logits that a product split along K left as partial sums
@@ -314,7 +327,8 @@ constexpr int SELECT_ROWS = 4;
 __global__ void __launch_bounds__(SELECT_ROWS * 32) router_select_partials_kernel(
     const float* __restrict__ partials, int n_partials, long long partial_stride, int ld, int T, int E, int k,
     int norm_topk, int* __restrict__ sel, float* __restrict__ w, float* __restrict__ shared_scale,
-    const int* __restrict__ pin, float* __restrict__ gap) {
+    const int* __restrict__ pin, float* __restrict__ gap,
+    const float* __restrict__ corr, float wscale) {
     cj::after_predecessor();
     cj::release_successor();
     __shared__ float probs[SELECT_ROWS][MAX_EXPERTS];
@@ -329,7 +343,7 @@ __global__ void __launch_bounds__(SELECT_ROWS * 32) router_select_partials_kerne
         row[warp][e] = v;
     }
     __syncwarp();
-    select_row(row[warp], t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane, pin, gap);
+    select_row(row[warp], t, E, k, norm_topk, sel, w, shared_scale, probs[warp], lane, pin, gap, corr, wscale);
 }
 
 // Counting sort of the picks (token t, choice j) by expert, stable.  One block per
@@ -411,9 +425,10 @@ __global__ void __launch_bounds__(GROUP_WARPS * 32) moe_group_kernel(
 // logits: scratch [T, E + 1] float32 (column E holds the shared gate's dot when a gate is given).
 // tickets: int32 [4], zero before the first use (the kernel leaves them zero); may be null, the two-launch form is then used.
 // pin: int32 [T, k] experts given instead of chosen, or null.  gap: float32 [T] routing margins out, or null.
+// correction: float32 [E] added to the scores for the choice alone, or null.  weight_scale: multiplies the picks' weights.
 CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* shared_gate, int T, int H, int E, int k,
                              int norm_topk, int* sel, float* w, float* shared_scale, float* logits, int* tickets,
-                             const int* pin, float* gap, cudaStream_t stream) {
+                             const int* pin, float* gap, const float* correction, float weight_scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!x || !Wr || !sel || !w || !logits || H <= 0) return CJ_ERR_ARG;
     if (shared_gate && !shared_scale) return CJ_ERR_ARG;
@@ -422,7 +437,7 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
     if (T <= 32 && tickets) {
         dim3 grid_small(n_cols, (T + SMALL_ROWS - 1) / SMALL_ROWS);
         cj::launch(router_small_kernel, dim3(grid_small), dim3(SMALL_ROWS * 32), 0, stream, x, Wr, shared_gate, T, H, E, k, norm_topk, logits, sel, w,
-                                                                         shared_gate ? shared_scale : nullptr, tickets, pin, gap);
+                                                                         shared_gate ? shared_scale : nullptr, tickets, pin, gap, correction, weight_scale);
         return launch_status();
     }
     // rows of x staged per block: as many as fit 200 KB of shared memory, at most 8
@@ -449,19 +464,19 @@ CJ_EXPORT int cj_router_topk(const float* x, const float* Wr, const float* share
     int st = launch_status();
     if (st) return st;
     cj::launch(router_select_kernel, dim3(T), dim3(32), 0, stream, logits, E, n_cols, k, norm_topk, sel, w, shared_gate ? shared_scale : nullptr,
-               pin, gap);
+               pin, gap, correction, weight_scale);
     return launch_status();
 }
 
 // partials: [n_partials][T][ld] float32 logits (column E the shared gate's dot when shared_scale is given).
 CJ_EXPORT int cj_router_select(const float* partials, int n_partials, long long partial_stride, int ld, int T, int E, int k,
                                int norm_topk, int* sel, float* w, float* shared_scale, const int* pin, float* gap,
-                               cudaStream_t stream) {
+                               const float* correction, float weight_scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!partials || !sel || !w || n_partials < 1) return CJ_ERR_ARG;
     if (E < 1 || E > MAX_EXPERTS || k < 1 || k > E || ld < E + (shared_scale ? 1 : 0)) return CJ_ERR_SIZE;
     cj::launch(router_select_partials_kernel, dim3((T + SELECT_ROWS - 1) / SELECT_ROWS), dim3(SELECT_ROWS * 32), 0, stream, 
-        partials, n_partials, partial_stride, ld, T, E, k, norm_topk, sel, w, shared_scale, pin, gap);
+        partials, n_partials, partial_stride, ld, T, E, k, norm_topk, sel, w, shared_scale, pin, gap, correction, weight_scale);
     return launch_status();
 }
 

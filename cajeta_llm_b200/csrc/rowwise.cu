@@ -372,6 +372,107 @@ CJ_EXPORT int cj_rmsnorm(float* x, const float* w, float eps, int rows, int H, v
 }
 
 // ---------------------------------------------------------------------------------
+// Dynamic Tanh, a norm that takes no statistic of the row: y = tanh(alpha x) w + b, with a scalar alpha,
+// a weight and a bias of the row's width, all float32.  Same outputs as the RMS norm above (the result in
+// the activation dtype, optionally its float32 copy or its three-term bfloat16 form; rows picked through
+// row_index; partial sums owed to x added first, x keeping the sum).  dyt_add is the same function on a
+// sublayer's result, added into the residual stream: hs += tanh(alpha y) w + b.  Elementwise, so a block takes
+// a row and its threads stride over it, four entries a thread where the row allows.
+// ---------------------------------------------------------------------------------
+template <typename TO, bool VEC>
+__global__ void dyt_kernel(float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float alpha, int H,
+                           TO* __restrict__ out, float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_split,
+                           const int* __restrict__ row_index, const float* __restrict__ partials, int n_partials,
+                           long long partial_stride) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int r = blockIdx.x;
+    float* src = x + (size_t)(row_index ? row_index[r] : r) * H;
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float4 v = *(const float4*)(src + i);
+            if (partials) {
+                for (int s = 0; s < n_partials; ++s) {
+                    const float4 p4 = *(const float4*)(partials + s * partial_stride + (size_t)r * H + i);
+                    v.x += p4.x; v.y += p4.y; v.z += p4.z; v.w += p4.w;
+                }
+                *(float4*)(src + i) = v;
+            }
+            const float4 w4 = *(const float4*)(w + i), b4 = *(const float4*)(b + i);
+            const float4 y = make_float4(fmaf(tanhf(alpha * v.x), w4.x, b4.x), fmaf(tanhf(alpha * v.y), w4.y, b4.y),
+                                         fmaf(tanhf(alpha * v.z), w4.z, b4.z), fmaf(tanhf(alpha * v.w), w4.w, b4.w));
+            store4<TO>(out + (size_t)r * H + i, y);
+            if (out_f32) *(float4*)(out_f32 + (size_t)r * H + i) = y;
+            if (out_split) write_split4(out_split + (size_t)r * 3 * H + i, H, y);
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = src[i];
+            if (partials) {
+                for (int s = 0; s < n_partials; ++s) v += partials[s * partial_stride + (size_t)r * H + i];
+                src[i] = v;
+            }
+            const float y = fmaf(tanhf(alpha * v), w[i], b[i]);
+            out[(size_t)r * H + i] = from_f32<TO>(y);
+            if (out_f32) out_f32[(size_t)r * H + i] = y;
+            if (out_split) write_split(out_split + (size_t)r * 3 * H + i, H, y);
+        }
+    }
+}
+
+template <bool VEC>
+__global__ void dyt_add_kernel(float* __restrict__ hs, const float* __restrict__ y, const float* __restrict__ w,
+                               const float* __restrict__ b, float alpha, int H) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const float* src = y + (size_t)blockIdx.x * H;
+    float* dst = hs + (size_t)blockIdx.x * H;
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            const float4 v = *(const float4*)(src + i), w4 = *(const float4*)(w + i), b4 = *(const float4*)(b + i);
+            float4 d = *(const float4*)(dst + i);
+            d.x += fmaf(tanhf(alpha * v.x), w4.x, b4.x);
+            d.y += fmaf(tanhf(alpha * v.y), w4.y, b4.y);
+            d.z += fmaf(tanhf(alpha * v.z), w4.z, b4.z);
+            d.w += fmaf(tanhf(alpha * v.w), w4.w, b4.w);
+            *(float4*)(dst + i) = d;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] += fmaf(tanhf(alpha * src[i]), w[i], b[i]);
+    }
+}
+
+CJ_EXPORT int cj_dyt(float* x, const float* w, const float* b, float alpha, int rows, int H, void* out, int out_dtype,
+                     float* out_f32, void* out_split, const int* row_index, const float* partials, int n_partials,
+                     long long partial_stride, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!x || !w || !b || !out || H <= 0) return CJ_ERR_ARG;
+    if (partials && (row_index || n_partials < 1)) return CJ_ERR_ARG;
+    const bool aligned = ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)b) | ((uintptr_t)out) | ((uintptr_t)out_f32) |
+                           ((uintptr_t)out_split) | ((uintptr_t)partials)) & 15) == 0;
+    const bool vec = H % 4 == 0 && aligned && (!partials || partial_stride % 4 == 0);
+    const int per = vec ? H / 4 : H;
+    const int threads = per >= 512 ? 256 : (per >= 128 ? 128 : 64);
+#define LAUNCH(TO, V) cj::launch(dyt_kernel<TO, V>, dim3(rows), dim3(threads), 0, stream, x, w, b, alpha, H, (TO*)out, out_f32, (__nv_bfloat16*)out_split, row_index, partials, n_partials, partial_stride)
+    if (out_dtype == CJ_F32) { if (vec) LAUNCH(float, true); else LAUNCH(float, false); }
+    else if (out_dtype == CJ_BF16) { if (vec) LAUNCH(__nv_bfloat16, true); else LAUNCH(__nv_bfloat16, false); }
+    else return CJ_ERR_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}
+
+CJ_EXPORT int cj_dyt_add(float* hs, const float* y, const float* w, const float* b, float alpha, int rows, int H, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!hs || !y || !w || !b || H <= 0) return CJ_ERR_ARG;
+    const bool vec = H % 4 == 0 && ((((uintptr_t)hs) | ((uintptr_t)y) | ((uintptr_t)w) | ((uintptr_t)b)) & 15) == 0;
+    const int per = vec ? H / 4 : H;
+    const int threads = per >= 512 ? 256 : (per >= 128 ? 128 : 64);
+    if (vec) cj::launch(dyt_add_kernel<true>, dim3(rows), dim3(threads), 0, stream, hs, y, w, b, alpha, H);
+    else cj::launch(dyt_add_kernel<false>, dim3(rows), dim3(threads), 0, stream, hs, y, w, b, alpha, H);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
 // Rotary encoding of q and k at each row's absolute position, fused with the write of
 // the rotated k and the raw v into the cache pages of the row's request.
 // Half-split pairs (d, d + rot/2): ang = float(p) * inv[d]; a' = a cos - b sin;

@@ -2,4 +2,4 @@
 from .base import (KvNeed, Part, Runtime, StateNeed, make_part, register_part, registered_parts,  # noqa: F401
                    unregister_part)
 from .plan import LayerSpec, ModelPlan, ParamSpec, PartSpec, ScheduleEntry  # noqa: F401
-from . import attention, block, composite, embedding, feed_forward, latent_attention, norm, position, recurrent, stream  # noqa: F401  (registration)
+from . import attention, block, composite, diff_attention, embedding, feed_forward, latent_attention, norm, position, recurrent, stream  # noqa: F401  (registration)

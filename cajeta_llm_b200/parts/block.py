@@ -27,7 +27,8 @@ request are per-request state.  The block therefore declares state itself (``sta
 convolution's share first, then the mixer's, which the mixer finds at ``entry.state_offset``.  Parameters:
 ``mixer_norm_name``, ``mixer_post_norm_name``, ``feed_forward_norm_name``, ``feed_forward_post_norm_name``,
 ``mixer_name``, ``feed_forward_name``, ``input_conv``, ``hidden_size``.  The post norms are the layer's norm
-specs (``mixer_norm`` / ``feed_forward_norm``) under their own names.
+specs (``mixer_norm`` / ``feed_forward_norm``) under their own names; any norm kind that offers ``add_normed(hs, y)``
+(the RMS norm, Dynamic Tanh) serves.
 """
 from __future__ import annotations
 
@@ -211,8 +212,8 @@ class SandwichBlock(Part):
             self.feed_forward_post_norm = make_part("norm", layer.feed_forward_norm, self.name(spec["feed_forward_post_norm_name"]), runtime)
             self.feed_forward = make_part("feed_forward", layer.feed_forward, self.name(spec["feed_forward_name"]), runtime)
         for n in (self.mixer_post_norm, self.feed_forward_post_norm):
-            if n is not None and not (hasattr(n, "weight") and hasattr(n, "eps")):
-                raise ValueError("a sandwich block takes post norms that are a weight and an eps (rmsnorm)")
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ValueError("a sandwich block takes post norms that can norm a sublayer's result into the stream (add_normed)")
         conv = dict(spec.get("input_conv") or {})
         self.taps = int(conv.get("taps", 1)) if conv else 1
         self.conv_name = self.name(conv["name"]) if conv else None
@@ -283,7 +284,7 @@ class SandwichBlock(Part):
         if pending is not None:
             y += pending.sum(dim=0)
         K.tag = "norm + add"
-        K.rmsnorm_add(hs, y, self.mixer_post_norm.weight, self.mixer_post_norm.eps)
+        self.mixer_post_norm.add_normed(hs, y)
         K.tag = None
         ff = self.feed_forward
         if ff is None:
@@ -294,5 +295,5 @@ class SandwichBlock(Part):
         y = torch.zeros_like(hs)
         ff.forward(x, x_exact, y, ctx)
         K.tag = "norm + add"
-        K.rmsnorm_add(hs, y, self.feed_forward_post_norm.weight, self.feed_forward_post_norm.eps)
+        self.feed_forward_post_norm.add_normed(hs, y)
         K.tag = None

@@ -1,9 +1,13 @@
-"""Feed-forward parts: the dense SwiGLU MLP and the sparse mixture of experts.
+"""Feed-forward parts: the dense SwiGLU MLP, a dense one with a squared ReLU, and the sparse mixture of experts.
 
 ``dense_swiglu``: ``W_d (silu(W_g x) * (W_u x))``, ``silu(x) = x / (1 + exp(-x))``
 (model/Prim.cajeta:1822-1847, model/CausalLM.cajeta:1556-1566).  Parameters:
 ``hidden_size``, ``intermediate_size``, ``names`` (optional: the tensor names of
 ``gate``, ``up`` and ``down`` under the part's prefix).
+
+``dense_relu2``: ``W_d max(W_u x, 0)^2``, a feed-forward without a gate whose activation is the square of the
+rectified sum.  Parameters: ``hidden_size``, ``intermediate_size``, ``names`` (``up``, ``down``).  On the tensor-core
+path the square is the up-product's epilogue (the float32 sum squared, then rounded); elsewhere a kernel of its own.
 
 ``sparse_moe``: router logits ``l_e = Wr[e] . x`` in float32, softmax over all experts,
 top-k by repeated strict-``>`` argmax (ties to the lower index), weights = the picked
@@ -33,7 +37,10 @@ the weight multiplying the float32 row before it is rounded for the products);
 ``route_groups`` ``(count, keep)``: the experts form ``count`` equal groups of neighbours, a group's
 score is its largest score, and only experts of the ``keep`` best groups can be picked;
 ``activation`` ``relu2``: an expert has no gate, ``W_d max(W_u x, 0)^2`` (tensors ``up`` and ``down`` only;
-built without a shared expert and with the weight on the output).
+built without a shared expert and with the weight on the output);
+``correction``: a tensor name, ``[num_experts]``: a number per expert that is added to its score for the CHOICE of the
+``top_k`` experts alone, a pick's weight staying its score without it; ``route_scale``: multiplies the picks'
+weights (after a renormalisation, when one is asked for).
 
 The file stores one tensor per expert and projection
 (``experts.{e}.gate_proj.weight`` ...); they are stacked into ``[E, I, H]`` and
@@ -94,6 +101,49 @@ class DenseSwiGLU(Part):
         K.tag = None
 
 
+@register_part("feed_forward", "dense_relu2")
+class DenseRelu2(Part):
+    needs_f32_input = False
+
+    def __init__(self, spec, prefix, runtime):
+        super().__init__(spec, prefix, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        names = dict(spec.get("names") or {})
+        self.n_up = self.name(names.get("up", "up_proj.weight"))
+        self.n_down = self.name(names.get("down", "down_proj.weight"))
+        self.w_up = self.w_down = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {self.n_up: ParamSpec((self.inter, self.hidden)), self.n_down: ParamSpec((self.hidden, self.inter))}
+
+    def libraries(self) -> set:
+        libs = {"gemm_simt", "recurrent"}
+        if self.runtime.fast_kernels and self.hidden >= 128:
+            libs |= {"gemm_tc", "gemm_tc2"}
+        return libs
+
+    def load(self, source) -> None:
+        self.w_up = self.fetch(source, self.n_up)
+        self.w_down = self.fetch(source, self.n_down)
+
+    def forward(self, x: torch.Tensor, x_f32: Optional[torch.Tensor], residual: torch.Tensor, ctx) -> None:
+        rt = self.runtime
+        T = x.shape[0]
+        act = torch.empty((T, self.inter), dtype=rt.act_dtype, device=x.device)
+        K.tag = "dense up"
+        if relu2_fused(rt, x, self.w_up, act.dtype):
+            project(rt, x, self.w_up, act, relu2=True)
+        else:
+            pre = torch.empty((T, self.inter), dtype=torch.float32, device=x.device)
+            project(rt, x, self.w_up, pre)
+            K.tag = "dense activation"
+            K.relu2_rows(pre, act)
+        K.tag = "dense down"
+        project(rt, act, self.w_down, residual, accumulate=True)
+        K.tag = None
+
+
 @register_part("feed_forward", "sparse_moe")
 class SparseMoE(Part):
     needs_f32_input = True      # the router reads the normed row in float32
@@ -124,6 +174,9 @@ class SparseMoE(Part):
         self.gated = self.activation == "swiglu"
         if not self.gated and (self.shared_inter > 0 or self.weight_on != "output" or self.act_limit > 0.0):
             raise ValueError("ungated experts are built without a shared expert, capped gates or the weight on the input")
+        self.n_correction = self.name(str(spec["correction"])) if spec.get("correction") else None
+        self.route_scale = float(spec.get("route_scale", 1.0))
+        self.correction = None
         groups = spec.get("route_groups")
         self.route_groups = (int(groups[0]), int(groups[1])) if groups and int(groups[0]) > 1 else None
         if self.route_groups:
@@ -153,6 +206,8 @@ class SparseMoE(Part):
 
     def params(self) -> Dict[str, ParamSpec]:
         p = {self.n_router: ParamSpec((self.num_experts, self.hidden), role="vector")}
+        if self.n_correction:
+            p[self.n_correction] = ParamSpec((self.num_experts,), role="vector", std=0.05)
         for e in range(self.num_experts):
             if self.gated:
                 p[self.expert_name("gate", e)] = ParamSpec((self.inter, self.hidden))
@@ -178,6 +233,8 @@ class SparseMoE(Part):
     def load(self, source) -> None:
         rt = self.runtime
         self.router = self.fetch(source, self.n_router)
+        if self.n_correction:
+            self.correction = self.fetch(source, self.n_correction)
 
         E, C, I = self.num_experts, self.shared_chunks, self.inter
 
@@ -261,10 +318,12 @@ class SparseMoE(Part):
             K.gemm_tc(x_exact, self.router_split, logits if splits > 1 else logits[0], K.EPI_STORE_F32, False, 128,
                       k_splits=splits)
             K.router_select(logits, self.num_experts, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap,
-                            sigmoid_scores=self.score == "sigmoid", groups=self.route_groups)
+                            sigmoid_scores=self.score == "sigmoid", groups=self.route_groups, correction=self.correction,
+                            weight_scale=self.route_scale)
         else:
             K.router_topk(x_exact, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap,
-                          sigmoid_scores=self.score == "sigmoid", groups=self.route_groups)
+                          sigmoid_scores=self.score == "sigmoid", groups=self.route_groups, correction=self.correction,
+                          weight_scale=self.route_scale)
 
     def forward(self, x: torch.Tensor, x_exact: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         rt = self.runtime

@@ -10,6 +10,7 @@ entries, values of ``vdim``, latent of ``kv_rank``::
     k_h = [W_uk[h] c | r] ,  v_h = W_uv[h] c
     score_h,j = (q_h[:dim] . W_uk[h] c_j + rotate(q_h[dim:], p) . r_j) * scale ,  j <= p
     out_h = sigmoid(W_g x)_h * sum_j softmax(score_h)_j v_h,j ;  then W_o on the heads
+    (the gate is optional, and so are a latent of the queries' own and a sink in the softmax: see the parameters)
 
 The rotation pairs entries (2i, 2i+1) of the first ``rotary_dim`` entries of the rotated
 part (the position part's ``rotary_dim`` and ``inv_freq``).  Nothing per head is built from
@@ -28,6 +29,14 @@ queries, ``W_uk`` and ``W_uv``.
 Parameters: ``hidden_size``, ``heads``, ``dim``, ``rot_dim``, ``vdim``, ``kv_rank``,
 ``scale``, ``eps``, ``position`` (a position PartSpec), ``owns_cache`` (false: no ``dkv``
 tensors).  Tensors: ``q``, ``g``, ``dkv``, ``dkv.norm``, ``uk``, ``uv``, ``o``.
+
+Optional, each off by default:
+``q_rank`` n > 0: the queries pass a latent of their own, ``c_q = rms(W_dq x) * w`` (``dq``, ``dq.norm``; the layer's
+eps), ``q = W_uq c_q`` (``uq``), instead of one projection ``q``; ``W_dq`` rides in the mixer's one input product,
+a kernel norms its columns, a second product brings the heads up;
+``gate`` false: no sigmoid gate on the heads' outputs (no tensor ``g``);
+``sink``: a tensor name, ``[heads]``: the softmax's divisor also holds ``exp(sink[h])``, a term without key or value
+that is neither scaled nor rotated and counts once.
 """
 from __future__ import annotations
 
@@ -57,6 +66,10 @@ class LatentAttention(Part):
         self.scale = float(spec["scale"])
         self.eps = float(spec["eps"])
         self.owns_cache = bool(spec.get("owns_cache", True))
+        self.q_rank = int(spec.get("q_rank", 0) or 0)
+        self.gate = bool(spec.get("gate", True))
+        self.n_sink = self.name(str(spec["sink"])) if spec.get("sink") else None
+        self.sink = self.w_qnorm = self.w_uq = None
         self.position = make_part("position", spec["position"], prefix, runtime)
         self.rotary = int(self.position.rotary_dim)
         if self.rotary > self.rot:
@@ -84,12 +97,20 @@ class LatentAttention(Part):
 
     def params(self) -> Dict[str, ParamSpec]:
         p = {
-            self.name("q"): ParamSpec((self.nq, self.hidden)),
-            self.name("g"): ParamSpec((self.heads, self.hidden)),
             self.name("uk"): ParamSpec((self.heads * self.dim, self.rank)),
             self.name("uv"): ParamSpec((self.heads * self.vdim, self.rank)),
             self.name("o"): ParamSpec((self.hidden, self.heads * self.vdim)),
         }
+        if self.q_rank:
+            p[self.name("dq")] = ParamSpec((self.q_rank, self.hidden))
+            p[self.name("dq.norm")] = ParamSpec((self.q_rank,), role="vector", init="ones")
+            p[self.name("uq")] = ParamSpec((self.nq, self.q_rank))
+        else:
+            p[self.name("q")] = ParamSpec((self.nq, self.hidden))
+        if self.gate:
+            p[self.name("g")] = ParamSpec((self.heads, self.hidden))
+        if self.n_sink:
+            p[self.n_sink] = ParamSpec((self.heads,), role="vector", std=1.0)
         if self.owns_cache:
             p[self.name("dkv")] = ParamSpec((self.rank + self.rot, self.hidden))
             p[self.name("dkv.norm")] = ParamSpec((self.rank,), role="vector", init="ones")
@@ -102,11 +123,19 @@ class LatentAttention(Part):
         return libs
 
     def load(self, source) -> None:
-        rows = [self.fetch(source, self.name("q")), self.fetch(source, self.name("g"))]
+        # the mixer's input product: (q, or the queries' latent) | (g) | (dkv), in this order
+        rows = [self.fetch(source, self.name("dq" if self.q_rank else "q"))]
+        if self.q_rank:
+            self.w_qnorm = self.fetch(source, self.name("dq.norm"))
+            self.w_uq = self.fetch(source, self.name("uq"))
+        if self.gate:
+            rows.append(self.fetch(source, self.name("g")))
+        if self.n_sink:
+            self.sink = self.fetch(source, self.n_sink)
         if self.owns_cache:
             rows.append(self.fetch(source, self.name("dkv")))
             self.w_norm = self.fetch(source, self.name("dkv.norm"))
-        self.w_in = torch.cat(rows, dim=0).contiguous()              # q | g | dkv: one product
+        self.w_in = torch.cat(rows, dim=0).contiguous()              # one product
         uk = self.fetch(source, self.name("uk"))
         # head h's W_uk^T as the weight of a product over dim: [heads, kv_rank, dim]
         self.w_uk_t = uk.view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
@@ -121,25 +150,39 @@ class LatentAttention(Part):
         write = entry.writes_cache
         if write and not self.owns_cache:
             raise ValueError(f"{self.prefix}: the plan lets this entry write a cache, but the part has no W_dkv")
-        n_out = self.nq + H + ((self.rank + self.rot) if write else 0)
+        n_q = self.q_rank or self.nq
+        gate_off = n_q
+        d_off = n_q + (H if self.gate else 0)
+        n_out = d_off + ((self.rank + self.rot) if write else 0)
         proj = torch.empty((T, n_out), dtype=torch.float32, device=dev)
         K.tag = "mixer in"
         project(rt, x, self.w_in[:n_out], proj)
+        q = proj                               # the heads' queries start at column 0 of this matrix
+        if self.q_rank:
+            cq = torch.empty((T, self.q_rank), dtype=rt.act_dtype, device=dev)
+            K.tag = "q latent norm"
+            K.latent_q_norm(proj, 0, self.q_rank, self.w_qnorm, self.eps, cq)
+            q = torch.empty((T, self.nq), dtype=torch.float32, device=dev)
+            K.tag = "q up"
+            project(rt, cq, self.w_uq, q)
+        gate = (proj, gate_off) if self.gate else (None, 0)
         inv_freq = self.position.inv_freq
         if write:
             K.tag = "latent norm + rope + cache write"
-            K.latent_kv_write(proj, self.nq + H, self.rank, self.rot, self.rotary, self.w_norm, self.eps, inv_freq,
+            K.latent_kv_write(proj, d_off, self.rank, self.rot, self.rotary, self.w_norm, self.eps, inv_freq,
                               ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens, entry.k_plane)
         if self.can_expand and T >= self.EXPAND_MIN_ROWS and not ctx.all_single and len(ctx.h_req_prior) > 0:
-            gated = self._plain_form(proj, ctx, entry)
+            gated = self._plain_form(q, gate, ctx, entry)
         else:
-            gated = self._absorbed_form(proj, ctx, entry)
+            gated = self._absorbed_form(q, gate, ctx, entry)
         K.tag = "o"
         project(rt, gated, self.w_o, residual, accumulate=True)
         K.tag = None
         return None
 
-    def _absorbed_form(self, proj: torch.Tensor, ctx, entry) -> torch.Tensor:
+    def _absorbed_form(self, proj: torch.Tensor, gate, ctx, entry) -> torch.Tensor:
+        """``proj``: float32 rows whose first ``heads * (dim + rot_dim)`` columns are the queries; ``gate``: (matrix, column)
+        of the heads' gate values, or (None, 0)."""
         rt = self.runtime
         dev = proj.device
         T, H = proj.shape[0], self.heads
@@ -161,16 +204,16 @@ class LatentAttention(Part):
         # stretches a row's keys are cut when the step has few rows.
         reach = ctx.max_context if ctx.all_single else entry.block_table.shape[1] * entry.page_tokens
         K.latent_attention(q_abs, q_rot, entry.k_plane, self.rank, self.rot, H, ctx.positions, ctx.row_req, entry.block_table,
-                           entry.page_tokens, self.scale, lat, max_context=reach)
+                           entry.page_tokens, self.scale, lat, max_context=reach, sink=self.sink)
         o = torch.empty((H * T, self.vdim), dtype=torch.float32, device=dev)
         K.tag = "value up"
         project(rt, lat, self.w_uv, o, group_offsets=offsets, max_group_rows=T, offsets_settled=True)
         gated = torch.empty((T, H * self.vdim), dtype=rt.act_dtype, device=dev)
-        K.tag = "head gate"
-        K.latent_gate_out(o, proj, self.nq, H, self.vdim, gated)
+        K.tag = "head gate" if gate[0] is not None else "heads out"
+        K.latent_gate_out(o, gate[0], gate[1], H, self.vdim, gated)
         return gated
 
-    def _plain_form(self, proj: torch.Tensor, ctx, entry) -> torch.Tensor:
+    def _plain_form(self, proj: torch.Tensor, gate, ctx, entry) -> torch.Tensor:
         rt = self.runtime
         dev = proj.device
         T, H = proj.shape[0], self.heads
@@ -206,8 +249,8 @@ class LatentAttention(Part):
         K.latent_q_pack(proj, H, self.dim, self.rot, self.rotary, self.position.inv_freq, ctx.positions, qx)
         ox = torch.empty((T, H, self.dv_pad), dtype=torch.bfloat16, device=dev)
         K.tag = "attention"
-        K.latent_flash(qx, ox, kx, vx, ctx.req_start, ctx.req_prior, req_base, ctx.n_requests, H, self.scale)
+        K.latent_flash(qx, ox, kx, vx, ctx.req_start, ctx.req_prior, req_base, ctx.n_requests, H, self.scale, sink=self.sink)
         gated = torch.empty((T, H * self.vdim), dtype=torch.bfloat16, device=dev)
-        K.tag = "head gate"
-        K.latent_gate_rows(ox, proj, self.nq, H, self.vdim, gated)
+        K.tag = "head gate" if gate[0] is not None else "heads out"
+        K.latent_gate_rows(ox, gate[0], gate[1], H, self.vdim, gated)
         return gated
