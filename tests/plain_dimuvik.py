@@ -68,11 +68,15 @@ def query_temperature(p: int, coef: float, every: int) -> float:
     return 1.0 + coef * math.log((p + 1) // every + 1)
 
 
+def projected(h: np.ndarray, w: Dict[str, np.ndarray], name: str) -> np.ndarray:
+    """W h + b, then the convolution over time when the tensor has one."""
+    u = h @ w[name].T + w[name + ".b"]
+    return causal_conv(u, w[name + ".conv"]) if name + ".conv" in w else u
+
+
 def differential_keys_values(h: np.ndarray, w: Dict[str, np.ndarray], pre: str):
     """Keys [T, G * 2 * dim] and values [T, G * vdim] after projection, bias and convolution."""
-    k = causal_conv(h @ w[pre + ".k"].T + w[pre + ".k.b"], w[pre + ".k.conv"])
-    v = causal_conv(h @ w[pre + ".v"].T + w[pre + ".v.b"], w[pre + ".v.conv"])
-    return k, v
+    return projected(h, w, pre + ".k"), projected(h, w, pre + ".v")
 
 
 def differential_attention(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, m: dict, eps: float, k: np.ndarray, v: np.ndarray) -> np.ndarray:
@@ -80,7 +84,7 @@ def differential_attention(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, m:
     T = h.shape[0]
     H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     diff, scale = float(m["diff"]), float(m["scale"])
-    q = causal_conv(h @ w[pre + ".q"].T + w[pre + ".q.b"], w[pre + ".q.conv"])
+    q = projected(h, w, pre + ".q")
     qt = m.get("q_temp")
     lam = (math.exp(float(np.sum(w[pre + ".lq1"] * w[pre + ".lk1"]))) - math.exp(float(np.sum(w[pre + ".lq2"] * w[pre + ".lk2"]))) + diff)
     out = np.zeros((T, H * vd))
@@ -108,13 +112,14 @@ def latent_cache(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, m: dict, eps
     return c, r
 
 
-def latent_attention(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, m: dict, eps: float) -> np.ndarray:
+def latent_attention(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, m: dict, eps: float, c: np.ndarray, r: np.ndarray) -> np.ndarray:
+    """Queries through their own latent, keys and values brought up per head from the cached latents ``c`` and the shared
+    rotated key parts ``r`` (this layer's own, or those of the layer whose cache it reads)."""
     T = h.shape[0]
     H, d, rd, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     scale = float(m["scale"])
     cq = rms(h @ w[pre + ".dq"].T, eps) * w[pre + ".dq.norm"]
     q = cq @ w[pre + ".uq"].T
-    c, r = latent_cache(h, w, pre, m, eps)
     ku = c @ w[pre + ".uk"].T          # [T, H * dim]
     vu = c @ w[pre + ".uv"].T          # [T, H * vdim]
     out = np.zeros((T, H * vd))
@@ -151,8 +156,10 @@ def route(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, ff: dict):
     return picks, weights
 
 
-def routed_feed_forward(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, ff: dict) -> np.ndarray:
+def routed_feed_forward(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, ff: dict, picks_out: Optional[dict] = None) -> np.ndarray:
     picks, weights = route(h, w, pre, ff)
+    if picks_out is not None:
+        picks_out[pre] = picks.tolist()
     out = np.zeros((h.shape[0], w[pre + ".e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for e, wt in zip(picks[t], weights[t]):
@@ -162,8 +169,10 @@ def routed_feed_forward(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, ff: d
     return out
 
 
-def forward(cfg: dict, w: Dict[str, np.ndarray], tokens: List[int], layer_outputs: Optional[list] = None) -> np.ndarray:
-    """Logits [T, vocab] of one sequence from position 0; ``layer_outputs`` collects the stream after every layer."""
+def forward(cfg: dict, w: Dict[str, np.ndarray], tokens: List[int], layer_outputs: Optional[list] = None,
+            picks: Optional[dict] = None) -> np.ndarray:
+    """Logits [T, vocab] of one sequence from position 0; ``layer_outputs`` collects the stream after every layer,
+    ``picks`` the chosen experts of every routed feed-forward by its tensor-name prefix."""
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][np.asarray(tokens)] * float(cfg.get("embedding", {}).get("scale", 1.0))
     kept = {}
@@ -177,14 +186,18 @@ def forward(cfg: dict, w: Dict[str, np.ndarray], tokens: List[int], layer_output
             k, v = kept[i if src is None else src]
             y = differential_attention(h, w, pre + ".mix", m, eps, k, v)
         elif layer["type"] == "latent_attention":
-            y = latent_attention(h, w, pre + ".mix", m, eps)
+            src = m.get("kv_from")
+            if src is None:
+                kept[i] = latent_cache(h, w, pre + ".mix", m, eps)
+            c, r = kept[i if src is None else src]
+            y = latent_attention(h, w, pre + ".mix", m, eps, c, r)
         else:
             raise ValueError(f"unknown layer type {layer['type']}")
         x = x + dyt(y, w, pre + ".norm1b")
         ff = layer.get("mlp")
         if ff is not None:
             h = dyt(x, w, pre + ".norm2")
-            y = dense_feed_forward(h, w, pre + ".mlp") if ff["kind"] == "dense" else routed_feed_forward(h, w, pre + ".mlp", ff)
+            y = dense_feed_forward(h, w, pre + ".mlp") if ff["kind"] == "dense" else routed_feed_forward(h, w, pre + ".mlp", ff, picks)
             x = x + dyt(y, w, pre + ".norm2b")
         if layer_outputs is not None:
             layer_outputs.append(x.copy())
@@ -214,6 +227,14 @@ def read_safetensors(path: str) -> Dict[str, np.ndarray]:
             raise ValueError(f"{name}: dtype {info['dtype']} is not read here")
         out[name] = arr.reshape(info["shape"])
     return out
+
+
+def greedy(cfg: dict, w: Dict[str, np.ndarray], prompt: List[int], n: int) -> List[int]:
+    """n tokens after the prompt, each the first largest logit."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(np.argmax(forward(cfg, w, toks)[-1])))
+    return toks[len(prompt):]
 
 
 def load_folder(model_dir: str):

@@ -1,0 +1,527 @@
+"""Dimuvik through the engine against the plain implementation (``plain_dimuvik.py``).
+
+Small configurations of their own whose sizes differ in every field (head groups, picked experts, taps and ranks
+that are neither 1 nor equal to one another, and some that are 1; values of another size than keys; a rotation over
+a part of the rotated entries; layers without a feed-forward; a layer that borrows another's keys and values).  Each
+mechanism alone as a small model; whole prompts against token-by-token decoding and portions down to two tokens;
+unequal requests in one batch against each alone; slots and pages used again; attention made sharp so that single
+keys - far ones, those at page borders, the first ones - decide a row, in prompts and in decoding; the steps of the
+query temperature; first tokens; long decoding; greedy generation through the entry point and its scheduler.
+"""
+import copy
+import json
+import os
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_dimuvik as P
+
+pytestmark = pytest.mark.gpu
+
+
+def moe(experts, top, ff, scale=1.7, shared=None):
+    d = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": scale}}
+    if shared:
+        d["shared"] = {"ff": shared}
+    return d
+
+
+def dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def latent(heads=3, dim=10, rot_dim=6, vdim=14, kv_rank=20, q_rank=12, dims=None, base=300.0, scale=0.3, kv_from=None, mlp=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+         "rot": {"base": base, "dims": rot_dim if dims is None else dims}, "scale": scale}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+
+
+def attn(heads=4, kv_heads=2, dim=6, vdim=10, conv=2, diff=0.35, scale=0.5, q_temp=(0.4, 7), kv_from=None, mlp=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "diff": diff, "scale": scale}
+    if conv:
+        m["conv"] = conv
+    if q_temp:
+        m["q_temp"] = {"coef": q_temp[0], "every": q_temp[1]}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+
+
+def config_of(layers, width=48, vocab=90, eps=1e-5, scale=2.0):
+    c = {"architecture": "Dimuvik", "width": width, "vocab": vocab, "norm": {"eps": eps}, "layers": copy.deepcopy(layers)}
+    if scale is not None:
+        c["embedding"] = {"scale": scale}
+    return c
+
+
+ALONE = {
+    "latent": [latent(mlp=None)],
+    "latent_part_rot": [latent(heads=2, dim=4, rot_dim=8, vdim=5, kv_rank=9, q_rank=7, dims=4, mlp=dense(40))],
+    "attention": [attn(mlp=None)],
+    "attention_one_tap": [attn(heads=3, kv_heads=3, dim=5, vdim=4, conv=1, q_temp=None, mlp=moe(5, 2, 12, shared=20))],
+    "borrowed": [attn(heads=6, kv_heads=2, dim=4, vdim=8, conv=4, mlp=dense(30)), latent(mlp=moe(7, 3, 10)),
+                 attn(heads=2, kv_heads=2, dim=4, vdim=8, conv=4, diff=0.8, q_temp=(0.9, 3), kv_from=0, mlp=None),
+                 latent(heads=5, dim=3, vdim=4, q_rank=5, kv_from=1, mlp=None)],
+}
+MIXED = [latent(mlp=dense(64)), attn(mlp=moe(6, 2, 16, shared=24)), latent(heads=2, dim=16, rot_dim=4, vdim=8, kv_rank=24, q_rank=20, dims=2, mlp=moe(4, 1, 20, scale=0.6)),
+         attn(heads=2, kv_heads=1, dim=8, vdim=16, conv=3, diff=0.6, scale=0.25, q_temp=(0.2, 16), mlp=dense(50)),
+         attn(heads=4, kv_heads=2, dim=6, vdim=10, conv=2, diff=0.1, q_temp=None, kv_from=1, mlp=None)]
+WIDE = [latent(heads=4, dim=32, rot_dim=32, vdim=32, kv_rank=128, q_rank=96, scale=0.12, mlp=moe(8, 2, 128, shared=192)),
+        attn(heads=4, kv_heads=2, dim=32, vdim=64, conv=3, scale=0.18, q_temp=(0.3, 50), mlp=dense(384)),
+        latent(heads=2, dim=64, rot_dim=16, vdim=64, kv_rank=64, q_rank=128, dims=8, scale=0.1, mlp=None),
+        attn(heads=6, kv_heads=2, dim=32, vdim=64, conv=3, scale=0.2, diff=0.7, q_temp=(0.3, 50), kv_from=1, mlp=moe(4, 3, 136))]
+CONFIGS = {
+    "mixed": config_of(MIXED),
+    "other": config_of([MIXED[3], MIXED[0], MIXED[2]], width=72, vocab=150, eps=1e-6, scale=None),
+    # wide enough for the tensor-core products of the bfloat16 path
+    "wide": config_of(WIDE, width=256, vocab=500, scale=1.5),
+}
+
+
+def louder(model_dir, sharp=1.0):
+    """The random-weights mode draws small values (standard deviation 0.02) and ones: every softmax would be flat, the
+    router near a tie everywhere, every norm's scalar 1.  What feeds scores, routers and gates is multiplied up so that
+    the mechanisms bite; ``sharp`` multiplies the queries further."""
+    from cajeta_llm_b200.weights.safetensors_io import Checkpoint, write_safetensors
+    ck = Checkpoint(model_dir)
+    tensors = {n: ck.load(n).float() for n in ck.names()}
+    ck.close()
+    for n, t in tensors.items():
+        leaf = n.split(".")[-1]
+        g = torch.Generator().manual_seed(len(n) + 7 * t.numel())
+        if leaf == "router":
+            t *= 15.0
+        elif leaf == "embed":
+            t *= 25.0                  # rows of the stream of order one: the first norm's tanh then works on its bend, not at zero
+        elif leaf in ("q", "uq", "dq"):
+            t *= 5.0 * sharp
+        elif leaf in ("k", "uk", "dkv"):
+            t *= 4.0 * (1.0 if sharp == 1.0 else 3.0)
+        elif leaf in ("up", "down", "v", "uv", "o", "gate"):
+            t *= 4.0
+        elif leaf == "alpha":
+            t.copy_(0.4 + 1.2 * torch.rand(t.shape, generator=g))
+        elif leaf in ("lq1", "lk1", "lq2", "lk2"):
+            t *= 4.0
+        elif leaf == "b" and t.numel() and n.split(".")[-2] in ("q", "k", "v"):
+            t.copy_(0.3 * torch.randn(t.shape, generator=g))
+        elif leaf in ("norm", "norm1", "norm2", "norm1b", "norm2b"):
+            t += 0.3 * torch.randn(t.shape, generator=g)
+    write_safetensors(os.path.join(model_dir, "model.safetensors"), {n: t.to(torch.bfloat16) for n, t in tensors.items()})
+
+
+def sharp(model_dir):
+    louder(model_dir, sharp=12.0)
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    made = {}
+
+    def get(name, raw, seed=5, touch=louder):
+        if name not in made:
+            d = str(tmp_path_factory.mktemp(f"dimuvik_{name}"))
+            helpers.write_model(d, raw, seed=seed)
+            if touch is not None:
+                touch(d)
+            made[name] = (d, P.load_folder(d))
+        return made[name]
+    return get
+
+
+def runner_for(model_dir, dtype, max_seqs=4, max_tokens=512, num_pages=None, cuda_graphs=True, page=16):
+    import cajeta_llm_b200  # noqa: F401
+    from cajeta_llm_b200.engine.model import load_model
+    from cajeta_llm_b200.engine.step import ModelRunner
+    from cajeta_llm_b200.parts.base import Runtime
+    model, _ = load_model(model_dir, Runtime(dtype, "cuda:0"))
+    return ModelRunner(model, page_tokens=page, max_seqs=max_seqs, max_tokens_per_seq=max_tokens,
+                       num_pages=num_pages if num_pages is not None else -(-max_tokens // page) * max_seqs, cuda_graphs=cuda_graphs)
+
+
+def oracle(cfg, W, tokens):
+    """The plain implementation's logits and its picks by the engine's routing keys."""
+    picks = {}
+    want = torch.from_numpy(P.forward(cfg, W, tokens, picks=picks))
+    return want, {k: torch.tensor(v, dtype=torch.int32) for k, v in picks.items()}
+
+
+def pin_rows(spans):
+    """A step's routing pin from [(request's picks, first position, count)] in the step's order."""
+    if not spans or not spans[0][0]:
+        return None
+    return {key: torch.cat([p[key][lo:lo + n] for p, lo, n in spans]).cuda().contiguous() for key in spans[0][0]}
+
+
+def feed(runner, slot, tokens, cuts, picks=None):
+    from cajeta_llm_b200.engine.step import StepEntry
+    out, at = [], 0
+    for n in cuts:
+        pin = pin_rows([(picks, at, n)]) if picks else None
+        out.append(runner.step([StepEntry(slot, tokens[at:at + n], list(range(n)))], routing_pin=pin).cpu())
+        at += n
+    assert at == len(tokens)
+    return torch.cat(out)
+
+
+def rel_err(got, want):
+    """Per row: RMS of the difference (mean taken off) over the RMS of the wanted logits."""
+    d = got.double() - want.double()
+    d = d - d.mean(dim=-1, keepdim=True)
+    w = want.double() - want.double().mean(dim=-1, keepdim=True)
+    return d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-9)
+
+
+def check(got, want, dtype, what, free_routing=False):
+    """float32: every row to rounding.  bfloat16 with the routing pinned: the median row within 5 % of the logits'
+    spread, at most a tenth of the rows (or three) beyond 12 %, none beyond 60 % (the weights are loud; a lost key or a
+    lost state moves most rows by the logits' whole spread, and the float32 runs hold every row).  With the routing free
+    a row near a tie may swap an expert: only the bulk is held."""
+    e = rel_err(got, want)
+    if dtype == "float32":
+        assert float(e.max()) < 1e-4, f"{what}: worst row {int(e.argmax())} differs by {float(e.max()):.2e}"
+        return
+    over = int((e > 0.12).sum())
+    allowed = max(3, int((0.2 if free_routing else 0.1) * e.numel()))
+    assert float(e.median()) < 5e-2 and over <= allowed and (free_routing or float(e.max()) < 0.6), \
+        f"{what}: median {float(e.median()):.3f}, worst {float(e.max()):.3f} (row {int(e.argmax())}), over 0.12: {over} of {e.numel()}"
+
+
+@pytest.mark.parametrize("name", sorted(ALONE))
+def test_each_mechanism_alone_as_a_small_model(folders, name):
+    d, (cfg, W) = folders(name, config_of(ALONE[name]), seed=3)
+    toks = helpers.random_tokens(90, 83, seed=1)
+    want, picks = oracle(cfg, W, toks)
+    for dtype in ("float32", "bfloat16"):
+        pins = picks if dtype == "bfloat16" else None
+        r = runner_for(d, dtype, max_tokens=96)
+        s = r.admit()
+        check(feed(r, s, toks, [83], pins), want, dtype, f"{name} whole {dtype}")
+        r.release(s)
+        s = r.admit()                                  # the same slot and pages again
+        check(feed(r, s, toks, [5, 2, 17, 2, 3, 30] + [1] * 24, pins), want, dtype, f"{name} portions {dtype}")
+
+
+def test_the_mechanisms_bite(folders):
+    """The tests' weights make every mechanism count: an oracle without one of them differs."""
+    d, (cfg, W) = folders("mixed", CONFIGS["mixed"], seed=7)
+    toks = helpers.random_tokens(cfg["vocab"], 90, seed=2)
+    want = torch.from_numpy(P.forward(cfg, W, toks))
+
+    def without(change):
+        c = copy.deepcopy(cfg)
+        w = dict(W)
+        change(c, w)
+        return float(rel_err(torch.from_numpy(P.forward(c, w, toks)), want)[30:].max())
+
+    mixer = lambda c, i: c["layers"][i]["mixer"]
+    assert without(lambda c, w: w.update({"l0.mix.sink": w["l0.mix.sink"] - 30.0})) > 1e-3            # no sink to speak of
+    assert without(lambda c, w: mixer(c, 2)["rot"].update(dims=4)) > 1e-3
+    assert without(lambda c, w: mixer(c, 0)["rot"].update(base=1e6)) > 1e-3
+    assert without(lambda c, w: w.update({"l0.mix.dq.norm": np.ones_like(w["l0.mix.dq.norm"])})) > 1e-3
+    assert without(lambda c, w: mixer(c, 1).update(diff=0.5)) > 1e-3
+    assert without(lambda c, w: mixer(c, 1).pop("q_temp")) > 1e-3
+    assert without(lambda c, w: mixer(c, 3)["q_temp"].update(every=5)) > 1e-3
+    assert without(lambda c, w: w.update({"l1.mix.lq1": 0.0 * w["l1.mix.lq1"]})) > 1e-3
+    assert without(lambda c, w: w.update({"l1.mix.k.conv": np.eye(2)[1][None, :].repeat(24, 0)})) > 1e-3
+    assert without(lambda c, w: w.update({"l1.mix.q.b": 0.0 * w["l1.mix.q.b"]})) > 1e-3
+    assert without(lambda c, w: mixer(c, 4).pop("kv_from") and None or w.update(
+        {"l4.mix." + k: w["l1.mix." + k][::-1].copy() for k in ("k", "k.b", "k.conv", "v", "v.b", "v.conv")})) > 1e-3
+    assert without(lambda c, w: w.update({"l1.mlp.correction": 0.0 * w["l1.mlp.correction"]})) > 1e-3
+    assert without(lambda c, w: c["layers"][1]["mlp"]["router"].update(scale=1.0)) > 1e-3
+    assert without(lambda c, w: c["layers"][1]["mlp"].pop("shared")) > 1e-3
+    assert without(lambda c, w: w.update({"l3.norm1b.alpha": np.asarray(1.0)})) > 1e-3
+    assert without(lambda c, w: w.update({"final.norm.b": 0.0 * w["final.norm.b"]})) > 1e-3
+    assert without(lambda c, w: c["embedding"].update(scale=1.0)) > 1e-3
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_decoded_and_in_portions(folders, name, dtype):
+    d, (cfg, W) = folders(name, CONFIGS[name], seed=7)
+    toks = helpers.random_tokens(cfg["vocab"], 150, seed=2)
+    want, picks = oracle(cfg, W, toks)
+    r = runner_for(d, dtype, max_tokens=160)
+    results = []
+    for cuts in ([150], [86] + [1] * 64, [2] * 75, [7, 2, 16, 3, 2, 9, 5, 2, 15, 14, 33, 2, 40]):
+        s = r.admit()
+        results.append(feed(r, s, toks, cuts))                       # routing free: steps replay from graphs in bfloat16
+        check(results[-1], want, dtype, f"{name} {dtype} cuts {cuts[:4]}", free_routing=True)
+        r.release(s)
+        if dtype == "bfloat16":
+            s = r.admit()
+            check(feed(r, s, toks, cuts, picks), want, dtype, f"{name} {dtype} cuts {cuts[:4]}, routing pinned")
+            r.release(s)
+    if dtype == "float32":
+        for other in results[1:]:                                    # the cut changes nothing but the rounding of sums
+            assert float(rel_err(other, results[0]).max()) < 2e-5
+
+
+def test_unequal_requests_in_one_batch_slots_and_pages_used_again(folders):
+    """Up to four live requests, portions of some beside single tokens of others, requests that sit a step
+    out, in a pool so small that pages and slots come back into use: every position equals the plain
+    implementation's."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    d, (cfg, W) = folders("mixed", CONFIGS["mixed"], seed=7)
+    rng = random.Random(4)
+    lens = [23, 48, 17, 64, 35, 29, 52, 2, 41, 1]
+    toks = {i: helpers.random_tokens(cfg["vocab"], n, seed=50 + i) for i, n in enumerate(lens)}
+    both = {i: oracle(cfg, W, t) for i, t in toks.items()}
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, max_seqs=4, max_tokens=64, num_pages=14)
+        waiting, live, got = list(toks), {}, {i: [] for i in toks}
+        while waiting or live:
+            while waiting and len(live) < 4:
+                i = waiting[0]
+                if sum(-(-(len(toks[j]) + 15) // 16) for j in live) + -(-(len(toks[i]) + 15) // 16) > 14:
+                    break
+                waiting.pop(0)
+                live[i] = [r.admit(), 0, max(1, len(toks[i]) - rng.randint(3, 12))]
+            entries, who, spans = [], [], []
+            for i, st in list(live.items()):
+                if len(live) > 1 and rng.random() < 0.2:
+                    continue
+                n = 1 if st[1] >= st[2] else min(rng.randint(2, 11), st[2] - st[1])
+                entries.append(StepEntry(st[0], toks[i][st[1]:st[1] + n], list(range(n))))
+                who.append((i, n))
+                spans.append((both[i][1], st[1], n))
+                st[1] += n
+            if not entries:
+                continue
+            out = r.step(entries, routing_pin=pin_rows(spans) if dtype == "bfloat16" else None).cpu()
+            at = 0
+            for i, n in who:
+                got[i].append(out[at:at + n])
+                at += n
+                if live[i][1] == len(toks[i]):
+                    r.release(live.pop(i)[0])
+        for i in toks:
+            check(torch.cat(got[i]), both[i][0], dtype, f"request {i} in the mixed batch ({dtype})")
+        r.cache.books.check()
+
+
+FAR = {
+    "latent": [latent(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=16, q_rank=8, base=10000.0, scale=0.6, mlp=None)],
+    "attention": [attn(heads=4, kv_heads=1, dim=16, vdim=8, conv=2, scale=0.6, q_temp=(0.5, 64), mlp=None)],
+    "borrowed": [attn(heads=2, kv_heads=2, dim=8, vdim=24, conv=3, scale=0.5, q_temp=(0.3, 100), mlp=None),
+                 attn(heads=4, kv_heads=2, dim=8, vdim=24, conv=3, scale=0.7, diff=0.2, q_temp=(0.6, 33), kv_from=0, mlp=None)],
+}
+
+
+@pytest.mark.parametrize("name", sorted(FAR))
+def test_far_keys_page_borders_and_the_first_keys(folders, name):
+    """Scores made sharp: a row's output is then close to the value of its best key, which for many rows lies hundreds of
+    tokens back, in another page and another chunk of keys, or among the very first.  Every row equals the plain
+    implementation's, whole, cut anywhere - at page borders and one token beside them - and decoded one by one; an
+    oracle that forgets the oldest keys is told apart by a wide margin."""
+    # a vocabulary large enough that a token seldom comes twice: keys that carry no position are then one of a kind
+    d, (cfg, W) = folders("far_" + name, config_of(FAR[name], width=32, vocab=2000), seed=9, touch=sharp)
+    toks = helpers.random_tokens(2000, 307, seed=5)
+    want = torch.from_numpy(P.forward(cfg, W, toks))
+    short = torch.from_numpy(P.forward(cfg, W, toks[40:]))
+    assert float(rel_err(short[160:], want[200:]).max()) > 0.1, "the test's weights do not show the far keys"
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, max_tokens=320)
+        for cuts in ([307], [300, 4] + [1] * 3, [17] * 18 + [1], [16, 1, 15, 32, 31, 2, 63, 64, 65] + [1] * 18):
+            s = r.admit()
+            check(feed(r, s, toks, cuts), want, dtype, f"far keys {dtype} cuts {cuts[:3]}")
+            r.release(s)
+
+
+def test_the_steps_of_the_query_temperature(folders):
+    """The temperature moves when floor((p + 1) / every) does: rows just before and just after such a position, in prompts
+    and decoded alone, against the plain implementation; an oracle whose step lies one token off differs."""
+    layer = attn(heads=2, kv_heads=1, dim=8, vdim=8, conv=2, scale=0.8, q_temp=(2.5, 13), mlp=None)
+    d, (cfg, W) = folders("temperature", config_of([layer], width=32, vocab=60), seed=11, touch=sharp)
+    toks = helpers.random_tokens(60, 70, seed=8)
+    want = torch.from_numpy(P.forward(cfg, W, toks))
+    for every in (12, 14):
+        off = copy.deepcopy(cfg)
+        off["layers"][0]["mixer"]["q_temp"]["every"] = every
+        assert float(rel_err(torch.from_numpy(P.forward(off, W, toks)), want).max()) > 0.02
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, max_tokens=96)
+        for cuts in ([70], [11, 1, 1, 1, 11, 1, 1, 12, 2, 12] + [1] * 17, [12, 13, 13, 14, 18], [1] * 70):
+            s = r.admit()
+            check(feed(r, s, toks, cuts), want, dtype, f"temperature {dtype} cuts {cuts[:4]}")
+            r.release(s)
+
+
+def test_first_tokens_and_long_decoding(folders):
+    d, (cfg, W) = folders("other", CONFIGS["other"], seed=7)
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, max_tokens=192)
+        for n in (1, 2, 3, 4, 6):
+            toks = helpers.random_tokens(cfg["vocab"], n, seed=20 + n)
+            s = r.admit()
+            check(feed(r, s, toks, [1] * n), oracle(cfg, W, toks)[0], dtype, f"{n} first tokens one by one ({dtype})", free_routing=True)
+            r.release(s)
+            s = r.admit()
+            check(feed(r, s, toks, [n]), oracle(cfg, W, toks)[0], dtype, f"{n} first tokens at once ({dtype})", free_routing=True)
+            r.release(s)
+        toks = helpers.random_tokens(cfg["vocab"], 183, seed=33)
+        s = r.admit()
+        check(feed(r, s, toks, [3] + [1] * 180), oracle(cfg, W, toks)[0], dtype, f"long decoding ({dtype})", free_routing=True)
+        r.release(s)
+
+
+def test_captured_steps_equal_uncaptured_ones(folders):
+    from cajeta_llm_b200.engine.step import StepEntry
+    d, (cfg, W) = folders("wide", CONFIGS["wide"], seed=7)
+    toks = [helpers.random_tokens(cfg["vocab"], 100, seed=70 + i) for i in range(3)]
+    outs = []
+    for graphs in (True, False):
+        r = runner_for(d, "bfloat16", max_tokens=128, cuda_graphs=graphs)
+        slots = [r.admit() for _ in toks]
+        got = []
+        for lo, hi in ((0, 12), (12, 24), (24, 36), (36, 48)):       # the same shape again and again: captured, then replayed
+            got.append(r.step([StepEntry(s, t[lo:hi], [hi - lo - 1]) for s, t in zip(slots, toks)]).cpu())
+        for i in range(48, 100):
+            got.append(r.step([StepEntry(s, [t[i]], [0]) for s, t in zip(slots, toks)]).cpu())
+        outs.append(torch.cat(got))
+        if graphs:
+            assert r.graph_replays > 0
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_long_prompts_on_the_tensor_core_attention(folders):
+    """Steps of some hundred rows on the bfloat16 path take the tiled attention kernels: a prompt of 700 tokens whole, in
+    portions of 300 and 256 beside a second request, and decoded on, against the plain implementation."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    d, (cfg, W) = folders("wide", CONFIGS["wide"], seed=7)
+    toks = helpers.random_tokens(cfg["vocab"], 700, seed=12)
+    other = helpers.random_tokens(cfg["vocab"], 40, seed=13)
+    want, picks = oracle(cfg, W, toks)
+    want_other, picks_other = oracle(cfg, W, other)
+    for dtype in ("bfloat16", "float32"):
+        pins = picks if dtype == "bfloat16" else None
+        r = runner_for(d, dtype, max_tokens=768, max_seqs=2)
+        s = r.admit()
+        check(feed(r, s, toks, [700], pins), want, dtype, f"700 tokens whole ({dtype})")
+        r.release(s)
+        s, s2 = r.admit(), r.admit()
+        got, got2, at = [], [], 0
+        for n, m in ((300, 17), (256, 1), (130, 22), (14, 0)):
+            entries = [StepEntry(s, toks[at:at + n], list(range(n)))]
+            spans = [(picks, at, n)]
+            lo = sum(g.shape[0] for g in got2)
+            if m:
+                entries.append(StepEntry(s2, other[lo:lo + m], list(range(m))))
+                spans.append((picks_other, lo, m))
+            out = r.step(entries, routing_pin=pin_rows(spans) if dtype == "bfloat16" else None).cpu()
+            got.append(out[:n])
+            if m:
+                got2.append(out[n:])
+            at += n
+        check(torch.cat(got), want, dtype, f"700 tokens in portions beside another request ({dtype})")
+        check(torch.cat(got2), want_other, dtype, f"the other request ({dtype})")
+
+
+def test_greedy_generation_through_the_entry_point_and_its_scheduler(folders):
+    from cajeta_llm_b200.engine.llm_engine import LlmEngine
+    from cajeta_llm_b200.engine.options import EngineOptions
+    from cajeta_llm_b200.sampling.params import SamplingParams
+    d, (cfg, W) = folders("mixed", CONFIGS["mixed"], seed=7)
+    prompts = [helpers.random_tokens(cfg["vocab"], n, seed=90 + n) for n in (5, 9, 17, 30, 3, 12)]
+    want = [P.greedy(cfg, W, p, 6) for p in prompts]
+    # more requests than slots, portions of at most 8 tokens under a budget of 24 a step
+    eng = LlmEngine.load(EngineOptions(model=d, dtype="float32", ctx=64, max_seqs=3, chunk=8, max_batch_tokens=24))
+    got = eng.generate(prompts, SamplingParams(max_new_tokens=6, stop_token_ids=()))
+    assert got == want
+    eng.close()
+    eng = LlmEngine.load(EngineOptions(model=d, dtype="bfloat16", ctx=64, max_seqs=4))
+    got = eng.generate(prompts, SamplingParams(max_new_tokens=6, stop_token_ids=()))
+    same = sum(g == w for g, w in zip(got, want))
+    assert same >= len(prompts) - 2, f"bfloat16 greedy tokens differ for {len(prompts) - same} prompts"
+    eng.close()
+
+
+def test_replay_tool_on_a_model_folder(folders, tmp_path):
+    d, (cfg, W) = folders("other", CONFIGS["other"], seed=7)
+    a, b = helpers.random_tokens(cfg["vocab"], 20, seed=1), helpers.random_tokens(cfg["vocab"], 9, seed=2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:11], "want": [10]}, {"id": "b", "tokens": b[:8], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[8:], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[11:], "want": [0, 8]}], "end": ["a"]}]
+    import subprocess
+    import sys
+    cmd = [sys.executable, os.path.join(helpers.ROOT, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out", str(tmp_path),
+           "--max-tokens", "128"]
+    proc = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    wa, wb = oracle(cfg, W, a)[0], oracle(cfg, W, b)[0]
+    got = {n: torch.from_numpy(np.fromfile(os.path.join(str(tmp_path), f"{n}.f32"), dtype="<f4").reshape(-1, cfg["vocab"])) for n in range(3)}
+    check(got[0], wa[10:11], "float32", "step 0")
+    check(got[1], wb[8:9], "float32", "step 1")
+    check(got[2], wa[[11, 19]], "float32", "step 2")
+
+
+def random_config(seed):
+    """A configuration drawn at random: layer order, every size and constant, who borrows whose cache."""
+    rng = random.Random(seed)
+    width = rng.choice([40, 72, 136, 256])
+    big = width >= 128
+
+    def pick(lo, hi):
+        return rng.randint(lo, hi)
+
+    layers = []
+    for i in range(rng.randint(1, 5)):
+        mlp = None
+        u = rng.random()
+        if u < 0.4:
+            experts = pick(1, 12)
+            mlp = moe(experts, pick(1, experts), rng.choice([pick(8, 60), 128, 136]) if big else pick(8, 60), scale=rng.choice([0.5, 1.0, 2.5]),
+                      shared=rng.choice([None, pick(8, 60), 128 if big else 24]))
+        elif u < 0.8:
+            mlp = dense(rng.choice([pick(8, 80), 256]) if big else pick(8, 80))
+        if rng.random() < 0.5:
+            kv = pick(1, 3)
+            owners = [j for j, l in enumerate(layers) if l["type"] == "attention" and "kv_from" not in l["mixer"]]
+            if owners and rng.random() < 0.4:
+                j = rng.choice(owners)
+                o = layers[j]["mixer"]
+                layer = attn(heads=o["kv_heads"] * pick(1, 3), kv_heads=o["kv_heads"], dim=o["dim"], vdim=o["vdim"], conv=o.get("conv"),
+                             diff=rng.choice([0.2, 0.5, 0.8]), scale=rng.choice([0.1, 0.3, 1.0]),
+                             q_temp=rng.choice([None, (0.3, pick(1, 40))]), kv_from=j, mlp=mlp)
+            else:
+                layer = attn(heads=kv * pick(1, 3), kv_heads=kv, dim=rng.choice([32, 64]) if big and rng.random() < 0.5 else pick(2, 24),
+                             vdim=rng.choice([32, 64, 128]) if big and rng.random() < 0.5 else pick(2, 40), conv=rng.choice([None, 1, 2, 3, 5]),
+                             diff=rng.choice([0.2, 0.5, 0.8]), scale=rng.choice([0.1, 0.3, 1.0]), q_temp=rng.choice([None, (0.3, pick(1, 40))]), mlp=mlp)
+        else:
+            owners = [j for j, l in enumerate(layers) if l["type"] == "latent_attention" and "kv_from" not in l["mixer"]]
+            if owners and rng.random() < 0.4:
+                j = rng.choice(owners)
+                o = layers[j]["mixer"]
+                layer = latent(heads=pick(1, 5), dim=pick(2, 24), rot_dim=o["rot_dim"], vdim=pick(2, 24), kv_rank=o["kv_rank"], q_rank=pick(2, 40),
+                               dims=o["rot"]["dims"], base=o["rot"]["base"], scale=rng.choice([0.1, 0.3]), kv_from=j, mlp=mlp)
+            else:
+                rot_dim = 2 * pick(1, 16)
+                layer = latent(heads=pick(1, 5), dim=rng.choice([32, 64]) if big and rng.random() < 0.5 else pick(2, 24), rot_dim=rot_dim,
+                               vdim=rng.choice([32, 64]) if big and rng.random() < 0.5 else pick(2, 24),
+                               kv_rank=rng.choice([64, 128]) if big and rng.random() < 0.5 else pick(4, 48), q_rank=pick(2, 40),
+                               dims=rot_dim if rng.random() < 0.6 else 2 * pick(1, rot_dim // 2), base=rng.choice([100.0, 10000.0, 500000.0]),
+                               scale=rng.choice([0.1, 0.3]), mlp=mlp)
+        layers.append(layer)
+    return config_of(layers, width=width, vocab=rng.choice([70, 131, 300]), eps=rng.choice([1e-5, 1e-6]), scale=rng.choice([None, 0.5, 3.0]))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(folders, seed):
+    raw = random_config(4000 + seed)
+    d, (cfg, W) = folders(f"random{seed}", raw, seed=100 + seed)
+    toks = helpers.random_tokens(cfg["vocab"], 120, seed=seed)
+    want, picks = oracle(cfg, W, toks)
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, max_tokens=128)
+        for cuts in ([120], [17, 2, 9, 60] + [1] * 32):
+            s = r.admit()
+            check(feed(r, s, toks, cuts, picks if dtype == "bfloat16" else None), want, dtype,
+                  f"{json.dumps(raw)} {dtype} cuts {cuts[:3]}")
+            r.release(s)
