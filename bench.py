@@ -241,7 +241,7 @@ def main() -> int:
     ap.add_argument("--timeline", action="store_true",
                     help="instead of the bench line: where one replayed decode step of --batch requests spends its time, kernel by "
                          "kernel, from the device's own timestamps (how much later each kernel ends than the one before it)")
-    ap.add_argument("--design", default="", choices=["", "balalorn", "saropel", "govuvik"],
+    ap.add_argument("--design", default="", choices=["", "balalorn", "saropel", "govuvik", "dimuvik"],
                     help="instead of the bench line: prefill and decode throughput of a model of this design at a few layer sizes, "
                          "beside the Qwen2-MoE model at equal sizes, one JSON line each (the default workload is untouched)")
     ap.add_argument("--sizes", default="small,medium,large", help="with --design: which of the sizes small, medium, large")

@@ -1,8 +1,9 @@
-"""Throughput of a Balalorn, a Saropel or a Govuvik model at layer sizes that resemble real models', beside the
+"""Throughput of a Balalorn, a Saropel, a Govuvik or a Dimuvik model at layer sizes that resemble real models', beside the
 engine's Qwen2-MoE model at equal width, depth, experts and feed-forward sizes (Govuvik: beside Balalorn, the
-engine's other model with recurrent state, at equal width, depth and experts).
+engine's other model with recurrent state, at equal width, depth and experts; Dimuvik: beside Balalorn, the engine's
+other model with attention over a latent and a borrowed cache, at equal width, depth, heads, latent and experts).
 
-``python bench.py --design balalorn|saropel|govuvik [--sizes small,medium,large]`` prints one JSON line per
+``python bench.py --design balalorn|saropel|govuvik|dimuvik [--sizes small,medium,large]`` prints one JSON line per
 (size, model): prefill tokens a second (one prompt of 2,048 tokens), decode tokens a second
 (8 requests of 512 tokens each, steps replayed from CUDA graphs), and where the time of both
 steps goes by class of work (launches serialised, an event behind each), with the bytes or
@@ -81,6 +82,25 @@ def govuvik_config(s):
             "layers": [kinds[i % 4]() for i in range(s["layers"])]}
 
 
+def dimuvik_config(s):
+    """Four layers: latent attention (queries through a latent of three times the keys' rank, a sink) + routed with a shared
+    expert, differential attention (H heads of two maps of 64 over H/2 key heads, values of 128, 4 taps, a query
+    temperature) + dense, latent attention + routed, differential attention on the second layer's keys and values + dense."""
+    h, H = s["width"], s["heads"]
+    latent = {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": s["rank"], "q_rank": 3 * s["rank"], "scale": (128 + 64) ** -0.5,
+              "rot": {"base": 10000.0, "dims": 64}}
+    diff = {"heads": H, "kv_heads": H // 2, "dim": 64, "vdim": 128, "conv": 4, "diff": 0.6, "scale": 64 ** -0.5,
+            "q_temp": {"coef": 0.1, "every": 1024}}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["experts"], "top": s["top"], "scale": 2.5}, "shared": {"ff": s["eff"]}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    kinds = [lambda i: {"type": "latent_attention", "mixer": dict(latent), "mlp": moe},
+             lambda i: {"type": "attention", "mixer": dict(diff), "mlp": dense},
+             lambda i: {"type": "latent_attention", "mixer": dict(latent), "mlp": moe},
+             lambda i: {"type": "attention", "mixer": dict(diff, kv_from=i - 2), "mlp": dense}]
+    return {"architecture": "Dimuvik", "width": h, "vocab": VOCAB, "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0},
+            "layers": [kinds[i % 4](i) for i in range(s["layers"])]}
+
+
 def qwen_config(s, shared=0):
     return {"architectures": ["Qwen2MoeForCausalLM"], "hidden_size": s["width"], "intermediate_size": s["ff"],
             "num_hidden_layers": s["layers"], "num_attention_heads": s["heads"], "num_key_value_heads": s["heads"], "head_dim": 128,
@@ -118,6 +138,14 @@ def needs(design, s, rows, ctx, prefill):
                        + rows * 4 * (n_mem * (H // 2) * (2 * 128 + 256 + 2) + n_par * (H // 4) * (3 * 128 + 256)),
                        rows * (n_mem * (H // 2) * 128 * 256 * 6 + n_par * (H // 4) * 128 * 256 * 5))
         return out
+    if design == "dimuvik":
+        n_lat, n_diff = (L + 3) // 4 + (L + 1) // 4, (L + 2) // 4 + L // 4
+        width = s["rank"] + 64
+        # both kinds under one class of work: the latent layers as for Balalorn; a differential layer reads a key head's
+        # [k1 | k2] and its value once a row (H/2 key heads of 128 + 128) and multiplies two maps of 64 and two value products
+        out["attention"] = ((rows * ctx * width * 2 * n_lat + rows * ctx * (H // 2) * (128 + 128) * 2 * n_diff) if not prefill else 0,
+                            (2 * H * (128 + 64 + 128) * n_lat + 2 * H * (2 * 64 + 2 * 128) * n_diff) * rows * (rows + 1) // 2 if prefill else 0)
+        return out
     n_lat, n_ssd, n_delta = (L + 3) // 4 + L // 4, (L + 2) // 4, (L + 1) // 4
     width = s["rank"] + 64
     # decode: the absorbed form reads each cache entry once; prompt portions: the plain form's flops
@@ -149,6 +177,8 @@ def run(args, peaks) -> int:
             pair = (("saropel", saropel_config(s)), ("qwen2_moe", qwen_config(s, shared=s["eff"])))
         elif args.design == "govuvik":
             pair = (("govuvik", govuvik_config(s)), ("balalorn", balalorn_config(s)))
+        elif args.design == "dimuvik":
+            pair = (("dimuvik", dimuvik_config(s)), ("balalorn", balalorn_config(s)))
         else:
             pair = (("balalorn", balalorn_config(s)), ("qwen2_moe", qwen_config(s)))
         for design, cfg in pair:

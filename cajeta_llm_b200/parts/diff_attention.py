@@ -108,6 +108,13 @@ class DifferentialAttention(Part):
             libs |= {"gemm_tc", "gemm_tc2"}
         return libs
 
+    def _tiled(self) -> bool:
+        """Whether attention runs in its tiled form (tensor cores): bfloat16 storage and sizes the form takes; float32
+        runs, and other sizes, take the row-at-a-time form."""
+        rt = self.runtime
+        return bool(rt.fast_kernels and rt.act_dtype == torch.bfloat16 and rt.cache_dtype == torch.bfloat16
+                    and K.diff_tile_shape(self.dim, self.vdim))
+
     def load(self, source) -> None:
         parts = self._projected()
         self.w_in = torch.cat([self.fetch(source, self.n[letter]) for letter, _ in parts], dim=0).contiguous()      # one product
@@ -152,9 +159,17 @@ class DifferentialAttention(Part):
                        q_temp_coef=self.temp_coef, q_temp_every=self.temp_every)
         out = torch.empty((T, self.heads, self.vdim), dtype=rt.act_dtype, device=dev)
         K.tag = "attention"
+        tiled = self._tiled() and hasattr(ctx, "req_start") and hasattr(ctx, "req_prior")
+        # how far a row's keys can reach, as a number that a captured step may keep: a decode step's context (its graph is
+        # keyed by the context's bucket), otherwise what the block table spans; it only decides into how many stretches a
+        # row block's keys are cut when the step has few rows
+        reach = 0
+        if tiled:
+            reach = ctx.max_context if getattr(ctx, "all_single", False) else entry.block_table.shape[1] * entry.page_tokens
         K.diff_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens,
                          self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.scale, self.lam, self.eps,
-                         1.0 - self.lambda_init)
+                         1.0 - self.lambda_init, req_start=ctx.req_start if tiled else None,
+                         req_prior=ctx.req_prior if tiled else None, n_requests=ctx.n_requests if tiled else 0, reach=reach)
         K.tag = "o"
         project(rt, out.view(T, self.o_dim), self.w_o, residual, accumulate=True)
         K.tag = None

@@ -525,3 +525,84 @@ def test_configurations_drawn_at_random(folders, seed):
             check(feed(r, s, toks, cuts, picks if dtype == "bfloat16" else None), want, dtype,
                   f"{json.dumps(raw)} {dtype} cuts {cuts[:3]}")
             r.release(s)
+
+
+def _differential_formula(q, keys, values, positions, row_req, window, scale, lam, eps, out_scale):
+    """The formula, row by row in float64.  q [T, H, 2 hd]; keys / values: per request [tokens, kv heads, 2 hd | vd]."""
+    T, H, kd = q.shape
+    hd = kd // 2
+    out = torch.zeros((T, H, values[0].shape[-1]), dtype=torch.float64)
+    for t in range(T):
+        p, kk, vv = int(positions[t]), keys[int(row_req[t])].double(), values[int(row_req[t])].double()
+        lo = max(0, p + 1 - window) if window > 0 else 0
+        G = kk.shape[1]
+        for h in range(H):
+            g = h // (H // G)
+            a = []
+            for mp in range(2):
+                s = (kk[lo:p + 1, g, mp * hd:(mp + 1) * hd] @ q[t, h, mp * hd:(mp + 1) * hd].double()) * scale
+                a.append(torch.softmax(s, dim=0) @ vv[lo:p + 1, g])
+            o = a[0] - lam * a[1]
+            out[t, h] = o / torch.sqrt((o * o).mean() + eps) * out_scale
+    return out
+
+
+@pytest.mark.parametrize("H,G,hd,vd,window,requests", [
+    (4, 2, 32, 64, 0, [(0, 40)]),
+    (8, 2, 64, 64, 0, [(0, 100), (50, 1), (7, 3), (0, 17)]),
+    (4, 4, 64, 128, 0, [(0, 150), (255, 1), (3, 2)]),
+    (6, 3, 32, 128, 0, [(0, 70), (63, 1), (64, 1), (65, 1), (127, 2)]),
+    (2, 1, 128, 128, 0, [(0, 130), (300, 1)]),
+    (2, 2, 128, 64, 37, [(0, 90), (36, 1), (37, 1), (38, 1), (200, 5)]),
+    (3, 1, 32, 64, 100, [(0, 260), (99, 1), (100, 1), (101, 1)]),
+])
+def test_tiled_differential_attention_against_the_formula(H, G, hd, vd, window, requests):
+    """The tensor-core form alone, on pages in a shuffled order: requests of (cached tokens, new rows), single rows at the
+    borders of a chunk of 64 keys and of a window, row blocks that end in the middle of a chunk, the keys dealt to one,
+    to three and to as many blocks as the library chooses.  Scores are loud, so that single keys decide rows; both the
+    tiled and the row-at-a-time form are held to the formula, and a window one key off is told apart."""
+    from cajeta_llm_b200.csrc import kernels as K
+    assert K.diff_tile_shape(hd, vd)
+    g = torch.Generator().manual_seed(H * 1000 + hd + vd)
+    page, dev = 16, "cuda"
+    totals = [p + r for p, r in requests]
+    pages_per = [(t + page - 1) // page for t in totals]
+    n_pages = sum(pages_per) + 3
+    order = torch.randperm(n_pages, generator=g)[:sum(pages_per)].int()
+    table = torch.full((len(requests), max(pages_per)), -1, dtype=torch.int32)
+    keys = [(torch.randn((t, G, 2 * hd), generator=g) * 0.7).bfloat16() for t in totals]
+    values = [torch.randn((t, G, vd), generator=g).bfloat16() for t in totals]
+    for kk in keys:
+        kk[::5] *= 3.0
+    kp, vp = torch.zeros((n_pages, G, page, 2 * hd), dtype=torch.bfloat16), torch.zeros((n_pages, G, page, vd), dtype=torch.bfloat16)
+    at = 0
+    for r, n in enumerate(pages_per):
+        table[r, :n] = order[at:at + n]
+        for t in range(totals[r]):
+            kp[int(table[r, t // page]), :, t % page] = keys[r][t]
+            vp[int(table[r, t // page]), :, t % page] = values[r][t]
+        at += n
+    q = torch.randn((sum(r for _, r in requests), H, 2 * hd), generator=g).bfloat16()
+    positions = torch.cat([torch.arange(p, p + r) for p, r in requests]).int()
+    row_req = torch.cat([torch.full((r,), i) for i, (_, r) in enumerate(requests)]).int()
+    starts = [0]
+    for _, r in requests:
+        starts.append(starts[-1] + r)
+    scale, lam, eps, out_scale = hd ** -0.5, 0.55, 1e-5, 0.4
+    want = _differential_formula(q, keys, values, positions, row_req, window, scale, lam, eps, out_scale)
+    reach = max(totals)
+    for splits in (None, 1, 3, "row at a time"):
+        got = torch.full((q.shape[0], H, vd), float("nan"), dtype=torch.bfloat16, device=dev)
+        tiled = splits != "row at a time"
+        K.diff_attention(q.to(dev), got, kp.to(dev), vp.to(dev), positions.to(dev), row_req.to(dev), table.to(dev), page, H, G, hd, vd,
+                         window, scale, lam, eps, out_scale,
+                         req_start=torch.tensor(starts, dtype=torch.int32, device=dev) if tiled else None,
+                         req_prior=torch.tensor([p for p, _ in requests], dtype=torch.int32, device=dev) if tiled else None,
+                         n_requests=len(requests) if tiled else 0, reach=reach, splits=splits if tiled else None)
+        err = (got.cpu().double() - want).abs()
+        assert float(err.max()) < 0.02 * max(1.0, float(want.abs().max())), \
+            f"{splits} shares: row {int(err.amax(dim=(1, 2)).argmax())} differs by {float(err.max()):.3g}"
+    if window > 0:
+        for other in (window + 1, window - 1):
+            moved = _differential_formula(q, keys, values, positions, row_req, other, scale, lam, eps, out_scale)
+            assert float((moved - want).abs().max()) > 0.05
