@@ -141,10 +141,12 @@ def needs(design, s, rows, ctx, prefill):
     if design == "dimuvik":
         n_lat, n_diff = (L + 3) // 4 + (L + 1) // 4, (L + 2) // 4 + L // 4
         width = s["rank"] + 64
-        # both kinds under one class of work: the latent layers as for Balalorn; a differential layer reads a key head's
-        # [k1 | k2] and its value once a row (H/2 key heads of 128 + 128) and multiplies two maps of 64 and two value products
-        out["attention"] = ((rows * ctx * width * 2 * n_lat + rows * ctx * (H // 2) * (128 + 128) * 2 * n_diff) if not prefill else 0,
-                            (2 * H * (128 + 64 + 128) * n_lat + 2 * H * (2 * 64 + 2 * 128) * n_diff) * rows * (rows + 1) // 2 if prefill else 0)
+        # the latent layers as for Balalorn; a differential layer reads a key head's [k1 | k2] and its value once a row
+        # (H/2 key heads of 128 + 128) and multiplies two maps of 64 and two value products of 128
+        out["attention"] = (rows * ctx * width * 2 * n_lat if not prefill else 0,
+                            2 * H * (128 + 64 + 128) * n_lat * rows * (rows + 1) // 2 if prefill else 0)
+        out["differential attention"] = (rows * ctx * (H // 2) * (128 + 128) * 2 * n_diff if not prefill else 0,
+                                         2 * H * (2 * 64 + 2 * 128) * n_diff * rows * (rows + 1) // 2 if prefill else 0)
         return out
     n_lat, n_ssd, n_delta = (L + 3) // 4 + L // 4, (L + 2) // 4, (L + 1) // 4
     width = s["rank"] + 64

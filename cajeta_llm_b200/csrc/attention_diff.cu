@@ -26,6 +26,7 @@
 //                           them together in stretch order, takes the difference and norms.
 // In both, how a row's keys are cut depends on the row's own range (and, in the split form, on a stretch length the
 // caller fixes for the step's shape), never on what else is in the batch.
+#define CJ_LIB "attention_diff"
 #include "common.cuh"
 
 using namespace cj;
@@ -215,8 +216,8 @@ __global__ void __launch_bounds__(FLASH_THREADS) diff_flash_kernel(
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ req_start, const int* __restrict__ req_prior,
     int n_requests, int T, const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window,
     float scale_log2, float lambda, float eps, float out_scale, int split_keys, float* __restrict__ partial) {
-    cj::after_predecessor();
-    cj::release_successor();
+    // launched in plain stream order (launch_in_order): everything before it has ended, and what follows starts when
+    // it has ended
     constexpr int KD = 2 * HD;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [BM][KD]
@@ -448,8 +449,6 @@ __global__ void __launch_bounds__(FLASH_THREADS) diff_flash_kernel(
 __global__ void __launch_bounds__(128) diff_merge_kernel(const float* __restrict__ partial, int splits, int split_keys, int T, int n_heads,
                                                          int vd, const int* __restrict__ positions, float lambda, float eps,
                                                          float out_scale, __nv_bfloat16* __restrict__ out) {
-    cj::after_predecessor();
-    cj::release_successor();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x, h = blockIdx.y * 4 + warp;
     if (h >= n_heads) return;
@@ -543,7 +542,7 @@ CJ_EXPORT int cj_diff_attention_tile(const void* q, void* out, const void* kplan
             if (e != cudaSuccess) return (int)e;                                                                         \
             configured = true;                                                                                           \
         }                                                                                                                \
-        cj::launch(diff_flash_kernel<H_, V_>, grid, dim3(FLASH_THREADS), smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, \
+        cj::launch_in_order(diff_flash_kernel<H_, V_>, grid, dim3(FLASH_THREADS), smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, \
                    (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, req_start, req_prior, n_requests, T, table,  \
                    table_stride, page_tokens, n_heads, n_kv, window, scale_log2, lambda, eps, out_scale, split_keys, part); \
     }
@@ -556,7 +555,7 @@ CJ_EXPORT int cj_diff_attention_tile(const void* q, void* out, const void* kplan
     else return CJ_ERR_SIZE;
 #undef LAUNCH
     if (split_keys > 0)
-        cj::launch(diff_merge_kernel, dim3(T, (n_heads + 3) / 4), dim3(128), 0, stream, (const float*)part, splits, split_keys, T, n_heads,
+        cj::launch_in_order(diff_merge_kernel, dim3(T, (n_heads + 3) / 4), dim3(128), 0, stream, (const float*)part, splits, split_keys, T, n_heads,
                    vd, positions, lambda, eps, out_scale, (__nv_bfloat16*)out);
     return launch_status();
 }

@@ -13,6 +13,7 @@
 // the block's warps take in turn, each keeping a running (max, sum, accumulator) as the
 // reference's flash kernels do (model/AttnKernel.cajeta:883); the cut depends only on
 // the row's own [from, p], so the result does not depend on the rest of the batch.
+#define CJ_LIB "attention_paged"
 #include "common.cuh"
 
 using namespace cj;

@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include <string.h>
 
 #define CJ_F32 0
 #define CJ_BF16 1
@@ -77,14 +78,22 @@ __device__ __forceinline__ float gated_act_fast(float g, float u, float limit, f
 __device__ __forceinline__ void after_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void release_successor() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// CAJETA_B200_SERIAL_LAUNCH=1 turns the overlap off (every kernel then starts after the one before has ended)
+// CAJETA_B200_SERIAL_LAUNCH=1 turns the overlap off (every kernel then starts after the one before has ended), and so
+// does cj_set_launch_overlap(0), which the engine calls for a model whose plan asks for plain stream order.
+// CAJETA_B200_SERIAL_LIBS=name,name turns it off for the kernels of the named libraries alone (a library names itself
+// with CJ_LIB before it includes this header): a way to find which neighbours' overlap a fault depends on.
+#ifndef CJ_LIB
+#define CJ_LIB "?"
+#endif
+static int g_launch_overlap = -1;      // -1: not asked yet; one copy a library
 inline bool overlap_launches() {
-    static int v = -1;
-    if (v < 0) {
+    if (g_launch_overlap < 0) {
         const char* e = getenv("CAJETA_B200_SERIAL_LAUNCH");
-        v = (e && e[0] == '1') ? 0 : 1;
+        g_launch_overlap = (e && e[0] == '1') ? 0 : 1;
+        const char* libs = getenv("CAJETA_B200_SERIAL_LIBS");
+        if (libs && strstr(libs, CJ_LIB)) g_launch_overlap = 0;
     }
-    return v != 0;
+    return g_launch_overlap != 0;
 }
 
 template <typename... P, typename... A>
@@ -102,9 +111,30 @@ inline void launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cud
     cudaLaunchKernelEx(&cfg, kernel, static_cast<A&&>(args)...);      // an error is left for launch_status()
 }
 
+// The same launch in plain stream order: the kernel starts when everything before it in the stream has ended.  For a
+// kernel that holds most of an SM for long (a successor set up beside it would only take room from its own later blocks);
+// such a kernel does not call release_successor() either, so what follows it starts when it has ended.
+template <typename... P, typename... A>
+inline void launch_in_order(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.numAttrs = 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<A&&>(args)...);
+}
+
 inline int launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;
 }
 
 }  // namespace cj
+
+// 0: this library's kernels launch in plain stream order from now on; 1: they may overlap their neighbours again
+// (unless the environment turned the overlap off)
+CJ_EXPORT void cj_set_launch_overlap(int on) {
+    if (!on) cj::g_launch_overlap = 0;
+    else { cj::g_launch_overlap = -1; cj::overlap_launches(); }
+}

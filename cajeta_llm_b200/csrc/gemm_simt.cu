@@ -13,6 +13,7 @@
 //     [offsets[g], offsets[g+1]) and its own weight slab W + g * w_group_stride;
 //     a_row_index maps a slot to its row of A (the token), as the reference's grouped
 //     forward gathers rows per expert (model/MoeFfn.cajeta:2644-2777).
+#define CJ_LIB "gemm_simt"
 #include "common.cuh"
 
 using namespace cj;

@@ -28,6 +28,7 @@
 // reference counterpart: the indirected per-expert GEMMs over (expert, row range) chunk
 // maps, io/WmmaKernel.cajeta (q4kWmmaIdMwKernel), and the dense projection GEMMs of
 // model/Linear.cajeta; both wmma-class there.
+#define CJ_LIB "gemm_tc"
 #include "common.cuh"
 #include "tc_common.cuh"
 

@@ -31,6 +31,7 @@
 //
 // reference counterpart: the same per-expert and dense projection GEMMs as the one-SM kernel
 // (io/WmmaKernel.cajeta, model/Linear.cajeta).
+#define CJ_LIB "gemm_tc2"
 #include "common.cuh"
 #include "tc_common.cuh"
 

@@ -26,6 +26,9 @@ class KernelError(RuntimeError):
 _libs: Dict[str, ctypes.CDLL] = {}
 
 
+_launch_overlap = True     # whether kernels may be set up beside the one before them in the stream (see set_launch_overlap)
+
+
 def library(name: str) -> ctypes.CDLL:
     """The loaded kernel library ``name`` (built first when it has to be)."""
     lib = _libs.get(name)
@@ -33,7 +36,20 @@ def library(name: str) -> ctypes.CDLL:
         path = _build.build(name)
         lib = ctypes.CDLL(path)
         _libs[name] = lib
+        if not _launch_overlap and hasattr(lib, "cj_set_launch_overlap"):
+            lib.cj_set_launch_overlap(_i(0))
     return lib
+
+
+def set_launch_overlap(on: bool) -> None:
+    """Whether a kernel may be set up on the SMs while the one before it in the stream is still draining (programmatic
+    dependent launch, the default) or every kernel starts when the one before has ended (plain stream order).  For all
+    libraries, those loaded later too; steps captured into CUDA graphs keep what held when they were captured."""
+    global _launch_overlap
+    _launch_overlap = bool(on)
+    for lib in _libs.values():
+        if hasattr(lib, "cj_set_launch_overlap"):
+            lib.cj_set_launch_overlap(_i(1 if on else 0))
 
 
 def loaded_libraries() -> Dict[str, str]:

@@ -20,6 +20,7 @@
 //
 // The rotation pairs entries (2i, 2i+1); the angle p * inv_freq[i] is float32.  Scores,
 // softmax and sums are float32 whatever the cache holds.
+#define CJ_LIB "latent_attention"
 #include "common.cuh"
 
 using namespace cj;

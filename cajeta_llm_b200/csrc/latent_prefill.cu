@@ -19,6 +19,7 @@
 // Token n of the dense buffers is (request tok_req[n], position tok_pos[n]); request i's
 // tokens lie at req_base[i] + position.  Rows are the step's rows: request i owns rows
 // [req_start[i], req_start[i+1]) at positions req_prior[i] + j.
+#define CJ_LIB "latent_prefill"
 #include "common.cuh"
 
 using namespace cj;

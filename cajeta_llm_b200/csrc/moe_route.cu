@@ -1,5 +1,6 @@
 // Routing of a mixture of experts: router logits, softmax and top-k, and the counting
 // sort of the picks by expert.  Everything here is float32.
+#define CJ_LIB "moe_route"
 #include "common.cuh"
 
 using namespace cj;

@@ -30,6 +30,7 @@
 // guard the staging of the tokens' inputs.  The tokens of a request are walked in order, which is what makes the result
 // independent of how a prompt was cut: the state after token t is the same sequence of
 // float32 operations whether t ended a step or not.
+#define CJ_LIB "recurrent"
 #include "common.cuh"
 
 using namespace cj;

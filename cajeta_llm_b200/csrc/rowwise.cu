@@ -1,6 +1,7 @@
 // Row-wise kernels: embedding gather, RMSNorm, rotary encoding fused with the write
 // of keys and values into cache pages, and the weighted combine of expert outputs.
 // All statistics, angles and sums are float32; storage is float32 or bfloat16.
+#define CJ_LIB "rowwise"
 #include "common.cuh"
 
 using namespace cj;

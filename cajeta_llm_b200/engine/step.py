@@ -151,6 +151,9 @@ class ModelRunner:
         # (``ctx.req_slot``, ``ctx.req_start``, ``ctx.row_req``, ``ctx.positions``: a captured step is
         # replayed with other values in them), reads nothing back on the host, and leaves alone the
         # requests a step's layout is filled up with (slot -1, no rows).
+        if self.runtime.device.type == "cuda":
+            from ..csrc import kernels as _K
+            _K.set_launch_overlap(getattr(model.plan, "launch_overlap", True))
         mixers = [model.blocks[e.layer].mixer for e in model.plan.schedule]
         graph_safe = all(getattr(m, "graph_safe", m.state_need() is None) for m in mixers)
         # a block that keeps state of its own (in front of its mixer's) answers for both

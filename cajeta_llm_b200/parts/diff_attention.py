@@ -158,7 +158,7 @@ class DifferentialAttention(Part):
                        self.heads, self.kv_heads, kd, self.vdim, 0, None, 1.0, None, None, 0.0, write,
                        q_temp_coef=self.temp_coef, q_temp_every=self.temp_every)
         out = torch.empty((T, self.heads, self.vdim), dtype=rt.act_dtype, device=dev)
-        K.tag = "attention"
+        K.tag = "differential attention"
         tiled = self._tiled() and hasattr(ctx, "req_start") and hasattr(ctx, "req_prior")
         # how far a row's keys can reach, as a number that a captured step may keep: a decode step's context (its graph is
         # keyed by the context's bucket), otherwise what the block table spans; it only decides into how many stretches a

@@ -109,6 +109,7 @@ class ModelPlan:
     max_position: Optional[int] = None
     embedding: PartSpec = PartSpec("token_embedding")     # how token ids become rows of the residual stream
     head: PartSpec = PartSpec("linear_head")              # how the normed wanted rows become logits
+    launch_overlap: bool = True          # False: this model's kernels launch in plain stream order, none set up beside its predecessor
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):
