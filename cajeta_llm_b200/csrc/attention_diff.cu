@@ -304,6 +304,11 @@ __global__ void __launch_bounds__(FLASH_THREADS) diff_flash_kernel(
         __syncthreads();
         const __nv_bfloat16* kb = ks + buf * BN * KD;
         const __nv_bfloat16* vb = vs + buf * BN * DV;
+        // a warp whose 16 rows lie past the block's rows (a single decoded token: all warps but one a map) only helps to load
+        if (wrow >= rows) {
+            __syncthreads();
+            continue;
+        }
 
         float s[BN / 8][4];
 #pragma unroll
