@@ -207,11 +207,13 @@ __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row,
     return base + row * D + chunk * 8 + (col & 7);
 }
 
-constexpr int BM = 64, BN = 64, FLASH_THREADS = 256;
+constexpr int BN = 64;      // keys a chunk
 
 // partial: [splits][T][n_heads][2][DV + 2] float32 (unnormalised sums, then the maximum in units of log 2 and the weight sum)
-template <int HD, int DV>
-__global__ void __launch_bounds__(FLASH_THREADS) diff_flash_kernel(
+// BM: rows a block (64 for steps with prompt portions; 16 for steps of single tokens, where a block is two warps, one a map,
+// and three blocks share a SM, each with a chunk of keys in flight)
+template <int HD, int DV, int BM>
+__global__ void __launch_bounds__(BM * 4) diff_flash_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kplane,
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ req_start, const int* __restrict__ req_prior,
     int n_requests, int T, const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window,
@@ -219,6 +221,8 @@ __global__ void __launch_bounds__(FLASH_THREADS) diff_flash_kernel(
     // launched in plain stream order (launch_in_order): everything before it has ended, and what follows starts when
     // it has ended
     constexpr int KD = 2 * HD;
+    constexpr int NW = BM / 16;                                     // warps a map
+    constexpr int FLASH_THREADS = 2 * NW * 32;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [BM][KD]
     __nv_bfloat16* ks = qs + BM * KD;                             // [2][BN][KD]
@@ -254,29 +258,36 @@ __global__ void __launch_bounds__(FLASH_THREADS) diff_flash_kernel(
     const int kt_begin = key_lo / BN, kt_end = key_hi / BN;         // key_lo > key_hi: a window that left this stretch behind
     const int* tab = table + (size_t)req * table_stride;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int mp = warp >> 2;                                       // the map this warp runs
-    const int wrow = (warp & 3) * 16;
+    const int mp = warp / NW;                                       // the map this warp runs
+    const int wrow = (warp % NW) * 16;
 
+    // where the keys of a chunk lie: the row of (page, key head, place in the page) in units of one cache entry, or -1 past the
+    // block's last key; worked out a chunk ahead by one thread a key, so that the copies below only read it
+    __shared__ int row_at[2][BN];
+    auto find_rows = [&](int kt) {
+        for (int r = tid; r < BN; r += FLASH_THREADS) {
+            const int key = kt * BN + r;
+            row_at[kt & 1][r] = key <= p_last ? (tab[key / page_tokens] * n_kv + kvh) * page_tokens + key % page_tokens : -1;
+        }
+    };
     auto load_kv = [&](int kt, int buf) {
         __nv_bfloat16* kd = ks + buf * BN * KD;
         __nv_bfloat16* vd = vs + buf * BN * DV;
+        const int* at = row_at[kt & 1];
         for (int i = tid; i < BN * CK; i += FLASH_THREADS) {
             const int r = i / CK, c = i % CK;
-            const int key = kt * BN + r;
-            const bool valid = key <= p_last;
-            size_t off = 0;
-            if (valid) off = (((size_t)tab[key / page_tokens] * n_kv + kvh) * page_tokens + key % page_tokens) * KD + c * 8;
-            cp_async16(kd + r * KD + (c ^ (r & 7)) * 8, kplane + off, valid);
+            const int row = at[r];
+            cp_async16(kd + r * KD + (c ^ (r & 7)) * 8, kplane + (row < 0 ? 0 : (size_t)row * KD + c * 8), row >= 0);
         }
         for (int i = tid; i < BN * CV; i += FLASH_THREADS) {
             const int r = i / CV, c = i % CV;
-            const int key = kt * BN + r;
-            const bool valid = key <= p_last;
-            size_t off = 0;
-            if (valid) off = (((size_t)tab[key / page_tokens] * n_kv + kvh) * page_tokens + key % page_tokens) * DV + c * 8;
-            cp_async16(vd + r * DV + (c ^ (r & 7)) * 8, vplane + off, valid);
+            const int row = at[r];
+            cp_async16(vd + r * DV + (c ^ (r & 7)) * 8, vplane + (row < 0 ? 0 : (size_t)row * DV + c * 8), row >= 0);
         }
     };
+    if (kt_begin <= kt_end) find_rows(kt_begin);
+    if (kt_begin < kt_end) find_rows(kt_begin + 1);
+    __syncthreads();
     for (int i = tid; i < BM * CK; i += FLASH_THREADS) {
         const int r = i / CK, c = i % CK;
         const bool valid = r < rows;
@@ -300,6 +311,8 @@ __global__ void __launch_bounds__(FLASH_THREADS) diff_flash_kernel(
         const int buf = (kt - kt_begin) & 1;
         if (kt < kt_end) load_kv(kt + 1, buf ^ 1);
         cp_async_commit();
+        // the rows of the chunk after the next: its slot was last read by this chunk's copies, a barrier ago
+        if (kt + 1 < kt_end) find_rows(kt + 2);
         cp_async_wait<1>();
         __syncthreads();
         const __nv_bfloat16* kb = ks + buf * BN * KD;
@@ -523,33 +536,40 @@ CJ_EXPORT int cj_diff_attention(const void* q, void* out, int act_dtype, const v
     return launch_status();
 }
 
-// The tiled form: bfloat16 everywhere, hd in {32, 64, 128}, vd in {64, 128}.  Request i owns rows [req_start[i], req_start[i+1])
+// The tiled form: bfloat16 everywhere, hd in {32, 64, 128}, vd in {64, 128}.  tile_rows: 64, or 16 for steps in which no request
+// brings more than 16 rows (single decoded tokens).  Request i owns rows [req_start[i], req_start[i+1])
 // at positions req_prior[i] + j.  split_keys > 0 (a multiple of 64): a row block's keys are dealt to `splits` blocks in stretches
 // of that many, partial [splits, T, n_heads, 2, vd + 2] float32 holds their shares, and a second kernel merges them.
 CJ_EXPORT int cj_diff_attention_tile(const void* q, void* out, const void* kplane, const void* vplane, const int* positions,
                                      const int* req_start, const int* req_prior, int n_requests, int T, const int* table,
                                      int table_stride, int page_tokens, int n_heads, int n_kv, int hd, int vd, int window, float scale,
                                      float lambda, float eps, float out_scale, int split_keys, int splits, float* partial,
-                                     cudaStream_t stream) {
+                                     int tile_rows, cudaStream_t stream) {
     if (T <= 0 || n_requests <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !positions || !req_start || !req_prior || !table) return CJ_ERR_ARG;
     if (n_heads <= 0 || n_heads > 65535 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0) return CJ_ERR_SIZE;
     if (split_keys < 0 || split_keys % BN != 0 || (split_keys > 0 && (splits < 1 || splits > 65535 || !partial))) return CJ_ERR_ARG;
+    if (tile_rows != 16 && tile_rows != 64) return CJ_ERR_SIZE;
     const float scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid((T + BM - 1) / BM + n_requests, n_heads, split_keys > 0 ? splits : 1);
+    dim3 grid((T + tile_rows - 1) / tile_rows + n_requests, n_heads, split_keys > 0 ? splits : 1);
     float* part = split_keys > 0 ? partial : nullptr;
-#define LAUNCH(H_, V_)                                                                                                   \
+#define LAUNCH_M(H_, V_, M_)                                                                                             \
     {                                                                                                                    \
-        size_t smem = (size_t)(BM * 2 * H_ + 2 * BN * 2 * H_ + 2 * BN * V_) * sizeof(__nv_bfloat16);                     \
+        size_t smem = (size_t)(M_ * 2 * H_ + 2 * BN * 2 * H_ + 2 * BN * V_) * sizeof(__nv_bfloat16);                     \
         static bool configured = false;                                                                                  \
         if (!configured) {                                                                                               \
-            cudaError_t e = cudaFuncSetAttribute(diff_flash_kernel<H_, V_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(diff_flash_kernel<H_, V_, M_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                                         \
             configured = true;                                                                                           \
         }                                                                                                                \
-        cj::launch_in_order(diff_flash_kernel<H_, V_>, grid, dim3(FLASH_THREADS), smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, \
+        cj::launch_in_order(diff_flash_kernel<H_, V_, M_>, grid, dim3(M_ * 4), smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, \
                    (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, req_start, req_prior, n_requests, T, table,  \
                    table_stride, page_tokens, n_heads, n_kv, window, scale_log2, lambda, eps, out_scale, split_keys, part); \
+    }
+#define LAUNCH(H_, V_)                                \
+    {                                                 \
+        if (tile_rows == 16) LAUNCH_M(H_, V_, 16)     \
+        else LAUNCH_M(H_, V_, 64)                     \
     }
     if (hd == 32 && vd == 64) LAUNCH(32, 64)
     else if (hd == 32 && vd == 128) LAUNCH(32, 128)
@@ -558,6 +578,7 @@ CJ_EXPORT int cj_diff_attention_tile(const void* q, void* out, const void* kplan
     else if (hd == 128 && vd == 64) LAUNCH(128, 64)
     else if (hd == 128 && vd == 128) LAUNCH(128, 128)
     else return CJ_ERR_SIZE;
+#undef LAUNCH_M
 #undef LAUNCH
     if (split_keys > 0)
         cj::launch_in_order(diff_merge_kernel, dim3(T, (n_heads + 3) / 4), dim3(128), 0, stream, (const float*)part, splits, split_keys, T, n_heads,

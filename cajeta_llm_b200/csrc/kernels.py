@@ -345,7 +345,7 @@ def diff_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_
                    row_req: torch.Tensor, table: torch.Tensor, page_tokens: int, n_heads: int, n_kv: int, head_dim: int,
                    value_dim: int, window: int, scale: float, lam: float, eps: float, out_scale: float,
                    req_start: Optional[torch.Tensor] = None, req_prior: Optional[torch.Tensor] = None, n_requests: int = 0,
-                   reach: int = 0, splits: Optional[int] = None) -> None:
+                   reach: int = 0, splits: Optional[int] = None, tile_rows: int = 64) -> None:
     """Differential attention of every row over its request's cached keys [from, position]: a query head is
     [q1 | q2] (``head_dim`` entries each), a cached key [k1 | k2]; each map is a softmax attention of its own over the
     same values, ``o = a1 - lam a2``, then ``o / sqrt(mean(o^2) + eps) * out_scale`` over the head's ``value_dim`` entries.
@@ -354,7 +354,8 @@ def diff_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_
     req_prior[i] + j), bfloat16 storage and sizes that :func:`diff_tile_shape` takes, the rows run in the tiled form: 64
     rows of a request and a head a block, the products on tensor cores.  ``reach``: a bound on the longest row's keys that
     the step's shape fixes; with few row blocks their keys are dealt to several blocks in stretches cut from it
-    (``splits``: how many, instead of as many as fill the machine)."""
+    (``splits``: how many, instead of as many as fill the machine).  ``tile_rows``: 64, or 16 when no request of the step brings
+    more than 16 rows (single decoded tokens): blocks of two warps, three of them a SM."""
     _need(q, "q"), _need(out, "out", q.dtype), _need(k_plane, "k_plane"), _need(v_plane, "v_plane", k_plane.dtype)
     _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
     T = q.shape[0]
@@ -365,9 +366,12 @@ def diff_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_
     if (req_start is not None and req_prior is not None and n_requests > 0 and q.dtype == torch.bfloat16
             and k_plane.dtype == torch.bfloat16 and diff_tile_shape(head_dim, value_dim)):
         _need(req_start, "req_start", torch.int32), _need(req_prior, "req_prior", torch.int32)
-        blocks = (-(-T // 64) + n_requests) * n_heads
+        if tile_rows not in (16, 64):
+            raise KernelError(f"diff_attention: tile_rows must be 16 or 64, found {tile_rows}")
+        blocks = (-(-T // tile_rows) + n_requests) * n_heads
+        fill = _sm_count() * (3 if tile_rows == 16 else 1)            # blocks that fill the machine
         if splits is None:
-            splits = min(32, -(-_sm_count() // blocks)) if blocks < _sm_count() else 1
+            splits = min(32, -(-fill // blocks)) if blocks < fill else 1
         split_keys, partial = 0, None
         if splits > 1 and reach > 128:
             split_keys = max(128, -(-(-(-reach // splits)) // 64) * 64)
@@ -379,7 +383,7 @@ def diff_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_
         st = library("attention_diff").cj_diff_attention_tile(
             _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(positions), _ptr(req_start), _ptr(req_prior), _i(n_requests), _i(T),
             _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_heads), _i(n_kv), _i(head_dim), _i(value_dim), _i(window),
-            _f(scale), _f(lam), _f(eps), _f(out_scale), _i(split_keys), _i(splits), _ptr(partial), _stream())
+            _f(scale), _f(lam), _f(eps), _f(out_scale), _i(split_keys), _i(splits), _ptr(partial), _i(tile_rows), _stream())
         _check(st, "diff_attention (tiled)")
         if split_keys:
             global launches

@@ -169,7 +169,8 @@ class DifferentialAttention(Part):
         K.diff_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens,
                          self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.scale, self.lam, self.eps,
                          1.0 - self.lambda_init, req_start=ctx.req_start if tiled else None,
-                         req_prior=ctx.req_prior if tiled else None, n_requests=ctx.n_requests if tiled else 0, reach=reach)
+                         req_prior=ctx.req_prior if tiled else None, n_requests=ctx.n_requests if tiled else 0, reach=reach,
+                         tile_rows=16 if getattr(ctx, "all_single", False) else 64)
         K.tag = "o"
         project(rt, out.view(T, self.o_dim), self.w_o, residual, accumulate=True)
         K.tag = None

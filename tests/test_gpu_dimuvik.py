@@ -555,6 +555,9 @@ def _differential_formula(q, keys, values, positions, row_req, window, scale, la
     (2, 1, 128, 128, 0, [(0, 130), (300, 1)]),
     (2, 2, 128, 64, 37, [(0, 90), (36, 1), (37, 1), (38, 1), (200, 5)]),
     (3, 1, 32, 64, 100, [(0, 260), (99, 1), (100, 1), (101, 1)]),
+    (8, 4, 64, 128, 0, [(511, 1), (63, 1), (64, 1), (700, 1), (0, 1), (130, 16)]),          # single tokens and a short portion
+    (4, 1, 128, 64, 50, [(300, 1), (49, 1), (50, 1), (51, 2)]),
+    (2, 2, 32, 128, 0, [(1000, 1)]),
 ])
 def test_tiled_differential_attention_against_the_formula(H, G, hd, vd, window, requests):
     """The tensor-core form alone, on pages in a shuffled order: requests of (cached tokens, new rows), single rows at the
@@ -591,17 +594,18 @@ def test_tiled_differential_attention_against_the_formula(H, G, hd, vd, window, 
     scale, lam, eps, out_scale = hd ** -0.5, 0.55, 1e-5, 0.4
     want = _differential_formula(q, keys, values, positions, row_req, window, scale, lam, eps, out_scale)
     reach = max(totals)
-    for splits in (None, 1, 3, "row at a time"):
+    small = max(r for _, r in requests) <= 16          # blocks of 16 rows take steps in which no request brings more
+    for splits, tile_rows in ((None, 64), (1, 64), (3, 64), ("row at a time", 64)) + (((None, 16), (1, 16), (4, 16)) if small else ()):
         got = torch.full((q.shape[0], H, vd), float("nan"), dtype=torch.bfloat16, device=dev)
         tiled = splits != "row at a time"
         K.diff_attention(q.to(dev), got, kp.to(dev), vp.to(dev), positions.to(dev), row_req.to(dev), table.to(dev), page, H, G, hd, vd,
                          window, scale, lam, eps, out_scale,
                          req_start=torch.tensor(starts, dtype=torch.int32, device=dev) if tiled else None,
                          req_prior=torch.tensor([p for p, _ in requests], dtype=torch.int32, device=dev) if tiled else None,
-                         n_requests=len(requests) if tiled else 0, reach=reach, splits=splits if tiled else None)
+                         n_requests=len(requests) if tiled else 0, reach=reach, splits=splits if tiled else None, tile_rows=tile_rows)
         err = (got.cpu().double() - want).abs()
         assert float(err.max()) < 0.02 * max(1.0, float(want.abs().max())), \
-            f"{splits} shares: row {int(err.amax(dim=(1, 2)).argmax())} differs by {float(err.max()):.3g}"
+            f"{splits} shares, blocks of {tile_rows} rows: row {int(err.amax(dim=(1, 2)).argmax())} differs by {float(err.max()):.3g}"
     if window > 0:
         for other in (window + 1, window - 1):
             moved = _differential_formula(q, keys, values, positions, row_req, other, scale, lam, eps, out_scale)
