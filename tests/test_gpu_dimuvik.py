@@ -390,6 +390,26 @@ def test_captured_steps_equal_uncaptured_ones(folders):
     assert torch.equal(outs[0], outs[1])
 
 
+def test_the_plan_s_launch_order_reaches_the_kernel_libraries(folders, tmp_path):
+    """A model whose plan asks for plain stream order turns the launch overlap off in every kernel library, and the next
+    model that allows it turns it on again; steps give the same logits either way."""
+    from cajeta_llm_b200.csrc import kernels as K
+    d, (cfg, W) = folders("wide", CONFIGS["wide"], seed=7)
+    toks = helpers.random_tokens(cfg["vocab"], 70, seed=4)
+    r = runner_for(d, "bfloat16", max_tokens=96)
+    assert K._launch_overlap is False
+    s = r.admit()
+    plain = feed(r, s, toks, [64, 6])
+    K.set_launch_overlap(True)
+    s2 = r.admit()
+    overlapped = feed(r, s2, toks, [64, 6])
+    assert torch.equal(plain, overlapped)
+    other = str(tmp_path / "qwen")
+    helpers.write_model(other, helpers.TINY_A, seed=3)
+    runner_for(other, "bfloat16", max_tokens=64)
+    assert K._launch_overlap is True
+
+
 def test_long_prompts_on_the_tensor_core_attention(folders):
     """Steps of some hundred rows on the bfloat16 path take the tiled attention kernels: a prompt of 700 tokens whole, in
     portions of 300 and 256 beside a second request, and decoded on, against the plain implementation."""
