@@ -89,9 +89,9 @@ def dimuvik_config(s):
     h, H = s["width"], s["heads"]
     latent = {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": s["rank"], "q_rank": 3 * s["rank"], "scale": (128 + 64) ** -0.5,
               "rot": {"base": 10000.0, "dims": 64}}
-    diff = {"heads": H, "kv_heads": H // 2, "dim": 64, "vdim": 128, "conv": 4, "diff": 0.6, "scale": 64 ** -0.5,
+    diff = {"heads": H, "kv_heads": H // 2, "dim": 64, "vdim": 128, "conv": 4, "diff": 0.5, "scale": 64 ** -0.5,
             "q_temp": {"coef": 0.1, "every": 1024}}
-    moe = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["experts"], "top": s["top"], "scale": 2.5}, "shared": {"ff": s["eff"]}}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["experts"], "top": s["top"], "scale": 2.0}, "shared": {"ff": s["eff"]}}
     dense = {"kind": "dense", "ff": s["ff"]}
     kinds = [lambda i: {"type": "latent_attention", "mixer": dict(latent), "mlp": moe},
              lambda i: {"type": "attention", "mixer": dict(diff), "mlp": dense},
