@@ -91,7 +91,9 @@ inline bool overlap_launches() {
         const char* e = getenv("CAJETA_B200_SERIAL_LAUNCH");
         g_launch_overlap = (e && e[0] == '1') ? 0 : 1;
         const char* libs = getenv("CAJETA_B200_SERIAL_LIBS");
-        if (libs && strstr(libs, CJ_LIB)) g_launch_overlap = 0;
+        const size_t n = strlen(CJ_LIB);
+        for (const char* at = libs ? strstr(libs, CJ_LIB) : nullptr; at; at = strstr(at + 1, CJ_LIB))      // whole names only
+            if ((at == libs || at[-1] == ',') && (at[n] == ',' || at[n] == 0)) g_launch_overlap = 0;
     }
     return g_launch_overlap != 0;
 }

@@ -510,7 +510,13 @@ int launch_pairs(Kern kern, int smem, long long total, cudaStream_t stream, cons
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = cj::overlap_launches() ? 2 : 1;
+    // A cluster kernel is launched in plain stream order: set up beside its predecessor (programmatic stream
+    // serialization) it stalled prompt steps now and then - one step in two to two hundred of some models never ended,
+    // and none in hundreds once these launches alone were taken out of the overlap, whatever else still overlapped.
+    // The kernel still releases its successor early (release_successor), which may be set up beside its tail.
+    // CAJETA_B200_PAIR_OVERLAP=1 puts the attribute back (to reproduce the stall).
+    static const bool pair_overlap = [] { const char* e = getenv("CAJETA_B200_PAIR_OVERLAP"); return e && e[0] == '1'; }();
+    cfg.numAttrs = (pair_overlap && cj::overlap_launches()) ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mx, mw, mw2, a, feat_tiles, tok_tiles, (int)total);
     if (e != cudaSuccess) return (int)e;
     return cj::launch_status();

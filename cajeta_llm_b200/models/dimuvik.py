@@ -218,11 +218,7 @@ def build_plan(cfg: DimuvikConfig) -> ModelPlan:
     plan = ModelPlan(architecture=cfg.architecture, hidden_size=h, vocab_size=cfg.vocab, embedding_name="embed",
                      layers=tuple(layers), schedule=tuple(schedule), final_norm=norm, final_norm_prefix="final.norm",
                      lm_head_name="head", eog_token_ids=cfg.eos_token_ids, max_position=None,
-                     embedding=PartSpec("token_embedding", {"scale": 0.0 if cfg.embedding_scale == 1.0 else cfg.embedding_scale}),
-                     # plain stream order: with launches overlapping, prompt steps of 2,048 rows of a four-layer model of this
-                     # design at width 2,048 stalled now and then (one step in two to eight), and never in hundreds of steps with
-                     # the overlap off; the cause is not known
-                     launch_overlap=False)
+                     embedding=PartSpec("token_embedding", {"scale": 0.0 if cfg.embedding_scale == 1.0 else cfg.embedding_scale}))
     plan.validate()
     return plan
 

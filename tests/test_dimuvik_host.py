@@ -59,7 +59,7 @@ def test_the_plan_follows_the_list_of_layers():
     ff = plan.layers[1].feed_forward
     assert (ff["top_k"], ff["route_scale"], ff["correction"], ff["shared_intermediate_size"], ff["norm_topk_prob"]) == (2, 1.7, "correction", 20, False)
     assert plan.layers[3].feed_forward["shared_intermediate_size"] == 0
-    assert plan.launch_overlap is False                      # this design's kernels launch in plain stream order
+    assert plan.launch_overlap is True
     assert cfg.to_json_dict() == RAW
 
 

@@ -390,24 +390,28 @@ def test_captured_steps_equal_uncaptured_ones(folders):
     assert torch.equal(outs[0], outs[1])
 
 
-def test_the_plan_s_launch_order_reaches_the_kernel_libraries(folders, tmp_path):
+def test_a_plan_s_launch_order_reaches_the_kernel_libraries(folders):
     """A model whose plan asks for plain stream order turns the launch overlap off in every kernel library, and the next
     model that allows it turns it on again; steps give the same logits either way."""
+    from dataclasses import replace
     from cajeta_llm_b200.csrc import kernels as K
+    from cajeta_llm_b200.engine.model import load_model
+    from cajeta_llm_b200.engine.step import ModelRunner
+    from cajeta_llm_b200.parts.base import Runtime
     d, (cfg, W) = folders("wide", CONFIGS["wide"], seed=7)
     toks = helpers.random_tokens(cfg["vocab"], 70, seed=4)
-    r = runner_for(d, "bfloat16", max_tokens=96)
+    model, _ = load_model(d, Runtime("bfloat16", "cuda:0"))
+    assert model.plan.launch_overlap
+    model.plan = replace(model.plan, launch_overlap=False)
+    r = ModelRunner(model, page_tokens=16, max_seqs=2, max_tokens_per_seq=96, num_pages=12)
     assert K._launch_overlap is False
     s = r.admit()
     plain = feed(r, s, toks, [64, 6])
-    K.set_launch_overlap(True)
-    s2 = r.admit()
-    overlapped = feed(r, s2, toks, [64, 6])
-    assert torch.equal(plain, overlapped)
-    other = str(tmp_path / "qwen")
-    helpers.write_model(other, helpers.TINY_A, seed=3)
-    runner_for(other, "bfloat16", max_tokens=64)
+    r2 = runner_for(d, "bfloat16", max_tokens=96)
     assert K._launch_overlap is True
+    s2 = r2.admit()
+    overlapped = feed(r2, s2, toks, [64, 6])
+    assert torch.equal(plain, overlapped)
 
 
 def test_long_prompts_on_the_tensor_core_attention(folders):
